@@ -22,7 +22,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function",
           "-ccbin", shutil.which("g++") or "g++"]
 # Kernels whose 32-bit mode must be exact to rounding (tanh / exp / division at full precision): no --use_fast_math.
-PRECISE = {"dense.cu", "attention_window.cu", "attention_diff.cu", "moe.cu"}
+PRECISE = {"dense.cu", "attention_window.cu", "attention_diff.cu", "moe.cu", "attention_latent.cu", "ssm_scan.cu", "postnorm.cu"}
 
 
 def _nvcc() -> str:

@@ -238,7 +238,7 @@ void attention_prefill_mma(float* out, const float* Q, const void* kc, const voi
 // two score maps per head, at least 16 queries.
 bool attention_window_mma_supported(int tokens, const WindowAttn& a, DType cache_dt) {
     const bool shape = (a.dim == a.vdim && (a.dim == 64 || a.dim == 128)) || (a.vdim == 2 * a.dim && (a.dim == 32 || a.dim == 64));
-    return cache_dt == DType::BF16 && shape && a.maps >= 1 && a.maps <= 2 && tokens >= 16 && a.kv_heads > 0 && a.heads % a.kv_heads == 0;
+    return cache_dt == DType::BF16 && shape && a.k_stride == 0 && a.v_stride == 0 && a.maps >= 1 && a.maps <= 2 && tokens >= 16 && a.kv_heads > 0 && a.heads % a.kv_heads == 0;
 }
 void attention_window_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int max_seq, const WindowAttn& a,
                           cudaStream_t s) {

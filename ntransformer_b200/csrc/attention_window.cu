@@ -25,7 +25,6 @@ namespace {
 
 constexpr int AW_WARPS = 8;
 constexpr int AW_MAX_SPLITS = 8;   // CTAs of one cluster sharing a (token, head): portable cluster size
-constexpr int AW_MAXV = 8;      // value elements per lane: vdim <= 256
 
 __device__ __forceinline__ float cache_ld(const float* p, size_t i) { return p[i]; }
 __device__ __forceinline__ float cache_ld(const __nv_bfloat16* p, size_t i) { return __uint_as_float((unsigned)reinterpret_cast<const unsigned short*>(p)[i] << 16); }
@@ -68,7 +67,7 @@ __device__ __forceinline__ float dot_row(const __nv_bfloat16* row, const float* 
 // Warps take groups of 32 visible keys.  Scoring is lane-per-key (each lane walks one key row against q in shared memory: no
 // cross-lane reduction per key); the group's maximum and the rescale are one warp reduction; the weighted value sum is
 // lane-per-channel (the 32 probabilities are broadcast one by one, value rows are read coalesced).
-template <typename KT>
+template <typename KT, int AW_MAXV>       // AW_MAXV: value elements per lane (vdim <= 32 * AW_MAXV)
 __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* __restrict__ out, const float* __restrict__ Q, const KT* __restrict__ kc,
                                                                          const KT* __restrict__ vc, const int* __restrict__ pos_dev, int p0,
                                                                          WindowAttn a) {
@@ -96,9 +95,10 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     const int lo = a.chunk > 0 ? (pos / a.chunk) * a.chunk : (a.window > 0 ? max(0, pos - a.window + 1) : 0);
     const int n_first = a.chunk > 0 ? 0 : min(a.keep, lo);
     const int n_keys = n_first + (pos - lo + 1);
-    const size_t kstride = (size_t)a.kv_heads * a.maps * a.dim, vstride = (size_t)a.kv_heads * a.vdim;
+    const size_t kstride = a.k_stride > 0 ? (size_t)a.k_stride : (size_t)a.kv_heads * a.maps * a.dim;
+    const size_t vstride = a.v_stride > 0 ? (size_t)a.v_stride : (size_t)a.kv_heads * a.vdim;
     constexpr int PER16 = 16 / (int)sizeof(KT);
-    const bool vec = a.dim % PER16 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;      // every key row then starts on 16 bytes
+    const bool vec = a.dim % PER16 == 0 && kstride % PER16 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;      // every key row then starts on 16 bytes
     float m = -FLT_MAX, l = 0.f, acc[AW_MAXV];
 #pragma unroll
     for (int e = 0; e < AW_MAXV; e++) acc[e] = 0.f;
@@ -222,7 +222,7 @@ void attention_window(float* out, const float* Q, const void* kc, const void* vc
                       int max_seq, const WindowAttn& a, cudaStream_t s) {
     static const bool no_mma = getenv("NT_B200_NO_WINDOW_MMA") != nullptr;
     if (!pos_dev && !no_mma && attention_window_mma_supported(tokens, a, cache_dt)) { attention_window_mma(out, Q, kc, vc, tokens, p0, max_seq, a, s); return; }
-    NT_CHECK(a.vdim <= 32 * AW_MAXV, "attention_window: value heads wider than 256 are not covered");
+    NT_CHECK(a.vdim <= 512, "attention_window: value heads wider than 512 are not covered");
     NT_CHECK(a.heads % a.kv_heads == 0, "attention_window: heads must be a multiple of kv_heads");
     NT_CHECK(cache_dt == DType::F32 || cache_dt == DType::BF16, "attention_window: F32 or BF16 cache");
     if (tokens <= 0) return;
@@ -240,11 +240,15 @@ void attention_window(float* out, const float* Q, const void* kc, const void* vc
     at[1].id = cudaLaunchAttributeClusterDimension;
     at[1].val.clusterDim.x = 1; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = (unsigned)splits;
     cfg.attrs = at; cfg.numAttrs = 2;
-    if (cache_dt == DType::F32)
-        NT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, attention_window_kernel<float>, out, Q, static_cast<const float*>(kc), static_cast<const float*>(vc), pos_dev, p0, a));
-    else
-        NT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, attention_window_kernel<__nv_bfloat16>, out, Q, static_cast<const __nv_bfloat16*>(kc),
-                                         static_cast<const __nv_bfloat16*>(vc), pos_dev, p0, a));
+    NT_CHECK(smem <= 48 * 1024, "attention_window: the head does not fit in shared memory");
+    const bool wide = a.vdim > 256;          // wide value rows (a latent as the value) keep 16 numbers per lane
+    if (cache_dt == DType::F32) {
+        auto* kern = wide ? attention_window_kernel<float, 16> : attention_window_kernel<float, 8>;
+        NT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, out, Q, static_cast<const float*>(kc), static_cast<const float*>(vc), pos_dev, p0, a));
+    } else {
+        auto* kern = wide ? attention_window_kernel<__nv_bfloat16, 16> : attention_window_kernel<__nv_bfloat16, 8>;
+        NT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, out, Q, static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), pos_dev, p0, a));
+    }
     count_launch();
 }
 

@@ -28,6 +28,9 @@ struct ModelConfig {                       // reference src/model/config.h:16-58
     float residual_mult = 1.0f;            // m of the PARALLEL block form
     int streams = 0;                       // STREAMS block form: residual streams (0: a single residual, no stream tensors)
     float embed_scale = 1.0f;              // the embedding row is multiplied by this
+    float norm_gain_offset = 0.0f;         // block / final norm gains are stored minus this (1: "zero-centred" gains); added once when the model is finalized
+    int side_dim = 0;                      // > 0: after every layer the token's own slice [layer * side_dim, +side_dim) of a second embedding table,
+                                           // gated by gelu(W_g x), projected back and RMS-normed, is added to the residual (POST_NORM form)
     bool layer_spec() const { return !layers.empty(); }
     void print() const;
 };

@@ -8,15 +8,22 @@
 namespace nt { namespace b200 {
 
 enum class MixerKind { ATTN_ROPE_CAUSAL = 0,     // rotary positions, full causal mask (the GGUF Llama block)
-                       ATTN_WINDOW = 1 };        // no positions in the scores; sliding window + kept first tokens; soft-capped scores
+                       ATTN_WINDOW = 1,          // no positions in the scores; sliding window + kept first tokens; soft-capped scores
+                       ATTN_LATENT = 2,          // queries and keys / values through low-rank latents; the cache holds the normed key / value latent
+                                                 // and one rotated key part shared by all heads; scored in the latent space (LatentSpec)
+                       SSM_SCAN = 3 };           // selective state-space recurrence with a short causal convolution in front (ScanSpec); no cache rows,
+                                                 // a fixed-size state per sequence instead
 enum class QKNorm { NONE = 0, WHOLE = 1 };       // WHOLE: one RMS norm across ALL heads of the projection (gain vector of that length)
 enum class GluAct { SILU = 0, GELU_TANH = 1 };
 enum class BlockForm { SEQUENTIAL = 0,           // x += mixer(norm1 x) ; x += ff(norm2 x)
                        PARALLEL = 1,             // h = norm1 x ; x += m * (ls1 * mixer(h) + ls2 * ff(h))
-                       STREAMS = 2 };            // SEQUENTIAL over several residual streams: a sublayer reads a learned blend of the streams and
+                       STREAMS = 2,              // SEQUENTIAL over several residual streams: a sublayer reads a learned blend of the streams and
                                                  // its output enters every stream through a learned stream-mixing matrix (ModelConfig::streams)
+                       POST_NORM = 3 };          // x += norm1(mixer(x)) ; x += norm2(ff(x)): the sublayers read x itself, the norm sits on their output
 enum class FfKind { GLU = 0,                     // W_down (act(W_gate h) * W_up h)
-                    MOE_RELU2 = 1 };             // routed experts W_down relu(W_up h)^2, top-k softmax over the chosen logits, optional gated shared expert
+                    MOE_RELU2 = 1,               // routed experts W_down relu(W_up h)^2, top-k softmax over the chosen logits, optional gated shared expert
+                    MOE_GLU = 2 };               // routed gated experts W_down (act(W_gate h) * W_up h); how they are chosen and weighted: RouteSpec
+
 
 // Rotary positions of one attention layer.  dims == 0: none.  The first `dims` channels of a head rotate, the rest pass.
 // factor > 0 selects the long-context blend: channel pairs whose wavelength is long against `original` positions are slowed by
@@ -27,6 +34,27 @@ struct RotarySpec {
     float base = 10000.f;
     bool interleaved = true;     // pairs (2i, 2i+1); false: (i, i + dims/2)
     float factor = 0.f, original = 0.f, fast = 0.f, slow = 0.f;
+};
+
+// Low-rank attention.  q = W_uq rms(W_dq h): per head [dim unrotated | rot_dim rotated].  W_dkv h = [kv_rank | rot_dim]: the first part,
+// RMS-normed, is the latent c; the second, rotated, is a key part common to all heads.  Head h's keys are [W_uk,h c | that part],
+// its values W_uv,h c.  The cache row of a position is [c | rotated part]: kv_rank + rot_dim numbers whatever the head count.
+struct LatentSpec {
+    int q_rank = 0, kv_rank = 0, rot_dim = 0;
+};
+// State-space scan.  W_in h = [z: inner | x: inner | B: groups*state | C: groups*state | dt: heads], inner = heads * vdim.  x, B, C pass a
+// causal per-channel convolution of `conv` taps and SiLU.  Per head: S <- exp(-exp(A_log) dt) S + dt B x^T (state x vdim), y = S^T C + D x,
+// dt = softplus(dt + dt_bias).  y * silu(z) is RMS-normed in `norm_groups` equal parts.  The state of a sequence is S plus the last
+// conv - 1 convolution inputs.
+struct ScanSpec {
+    int state = 0, groups = 1, conv = 0, norm_groups = 1;
+};
+// How a mixture of experts chooses and weights.  sigmoid: scores are sigmoid(logit) (else softmax over the chosen logits);
+// correction: a per-expert vector added to the scores for the CHOICE only; groups > 0: experts form `groups` equal runs of
+// neighbours, a run scores the sum of its two largest choice scores and only the best `keep` runs can be chosen from.
+struct RouteSpec {
+    bool sigmoid = false, correction = false;
+    int groups = 0, keep = 0;
 };
 
 struct LayerSpec {
@@ -54,6 +82,11 @@ struct LayerSpec {
     FfKind ff_kind = FfKind::GLU;
     int experts = 0, top = 0;    // MOE_RELU2: routed experts of width ff, experts used per token
     int shared_ff = 0;           // MOE_RELU2: width of the shared expert (0 = none); its output is scaled by sigmoid(<w_sg, h>)
+    // ---- mechanisms added with the Tanolorn family ----
+    LatentSpec latent;           // ATTN_LATENT (heads, dim, vdim, scale, rot and kv_from above apply too)
+    ScanSpec scan;               // SSM_SCAN (heads and vdim above apply too)
+    RouteSpec route;             // MOE_GLU
+    bool ff_bias = false;        // GLU: every projection has a bias vector
 };
 
 }}  // namespace nt::b200

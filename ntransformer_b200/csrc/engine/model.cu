@@ -77,10 +77,12 @@ Model::~Model() {
     for (size_t i = 0; i < kcs_.size(); i++) if (kcs_[i] && (cache_owned_.empty() || cache_owned_[i])) { cudaFree(kcs_[i]); cudaFree(vcs_[i]); }
     for (void* p : {(void*)pf_.h, (void*)pf_.tmp, pf_.hws, (void*)want_out_, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt,
                     (void*)pf_.sgate, (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)streams_, (void*)sub_y_, (void*)maps_out_, (void*)moe_sel_,
-                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_, (void*)pf_.g2, pf_.moe_ws})
+                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_, (void*)pf_.g2, pf_.moe_ws, (void*)pf_.gate_rows})
         if (p) cudaFree(p);
     if (moe_offsets_host_) cudaFreeHost(moe_offsets_host_);
-    for (LayerWeights& L : layers_) for (void* p : {(void*)L.e_up_tab, (void*)L.e_down_tab, (void*)L.rot_freq}) if (p) cudaFree(p);
+    for (LayerWeights& L : layers_)
+        for (void* p : {(void*)L.e_up_tab, (void*)L.e_down_tab, (void*)L.rot_freq, (void*)L.e_gate_tab, (void*)L.conv_state, (void*)L.ssm_state}) if (p) cudaFree(p);
+    for (void* p : {(void*)dec_.y, (void*)dec_.t[0], (void*)dec_.t[1], (void*)dec_.t[2], (void*)dec_.t[3], (void*)dec_.t[4]}) if (p) cudaFree(p);
     if (argmax_host_) cudaFreeHost(argmax_host_);
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -408,8 +410,11 @@ void Model::clear_kv() {
             const LayerSpec& L = cfg_.layers[(size_t)i];
             const size_t es = dtype_size(cache_dt_);
             if (!cache_owned_[(size_t)i]) continue;
-            NT_CUDA_CHECK(cudaMemsetAsync(kcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.maps * L.dim, stream_));
-            NT_CUDA_CHECK(cudaMemsetAsync(vcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.vdim, stream_));
+            (void)L;
+            size_t kw = 0, vw = 0;
+            cache_row_widths(i, kw, vw);
+            if (kcs_[(size_t)i]) NT_CUDA_CHECK(cudaMemsetAsync(kcs_[(size_t)i], 0, es * cfg_.max_seq_len * kw, stream_));
+            if (vcs_[(size_t)i]) NT_CUDA_CHECK(cudaMemsetAsync(vcs_[(size_t)i], 0, es * cfg_.max_seq_len * vw, stream_));
         }
         return;
     }
@@ -424,6 +429,10 @@ size_t Model::weight_bytes() const {
         for (int i = 0; i < cfg_.n_layers; i++) {
             const LayerWeights& L = layer_weights(i);
             b += L.wq.bytes() + L.wk.bytes() + L.wv.bytes() + L.wo.bytes() + L.gate.bytes() + L.up.bytes() + L.down.bytes();
+            b += L.w_dq.bytes() + L.w_uq.bytes() + L.w_dkv.bytes() + L.w_uk.bytes() + L.w_uv.bytes() + L.ssm_in.bytes() + L.side_gate.bytes() + L.side_proj.bytes();
+            if (cfg_.layers[(size_t)i].ff_kind == FfKind::MOE_GLU && cfg_.layers[(size_t)i].ff > 0)
+                b += (size_t)cfg_.layers[(size_t)i].experts * cfg_.hidden_size * 4 +
+                     (size_t)cfg_.layers[(size_t)i].top * (L.e_gate[0].bytes() + L.e_up[0].bytes() + L.e_down[0].bytes());
             // a decoded token reads the router, `top` of the experts and the shared expert
             const LayerSpec& S = cfg_.layers[(size_t)i];
             if (S.ff_kind == FfKind::MOE_RELU2 && S.ff > 0)
@@ -438,8 +447,13 @@ size_t Model::weight_bytes() const {
 size_t Model::bytes_per_token(int ctx) const {
     if (cfg_.layer_spec()) {
         size_t b = weight_bytes();
-        for (const LayerSpec& L : cfg_.layers)
-            b += (size_t)std::min(ctx, L.chunk > 0 ? L.chunk : (L.window > 0 ? L.window + L.keep_first : ctx)) * L.kv_heads * (L.maps * L.dim + L.vdim) * dtype_size(cache_dt_);
+        for (int i = 0; i < cfg_.n_layers; i++) {
+            const LayerSpec& L = cfg_.layers[(size_t)i];
+            size_t kw = 0, vw = 0;
+            cache_row_widths(L.kv_from >= 0 ? L.kv_from : i, kw, vw);
+            b += (size_t)std::min(ctx, L.chunk > 0 ? L.chunk : (L.window > 0 ? L.window + L.keep_first : ctx)) * (kw + vw) * dtype_size(cache_dt_);
+            if (L.mixer == MixerKind::SSM_SCAN) b += (size_t)2 * L.heads * L.vdim * L.scan.state * 4;      // the state is read and written
+        }
         return b;
     }
     return weight_bytes() + (size_t)2 * cfg_.n_layers * ctx * nkv_l_ * cfg_.head_dim * 2;

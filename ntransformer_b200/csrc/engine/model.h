@@ -53,6 +53,21 @@ struct LayerWeights {
     const void** e_down_tab = nullptr;
     float* rot_freq = nullptr;             // device, rot.dims / 2 angular frequencies (long-context blend applied), made at finalize
     float rot_mag = 1.f;
+    // low-rank attention (LatentSpec): query latent down / up, key-value latent down, per-head key / value up; gains of the two latents
+    Weight w_dq, w_uq, w_dkv, w_uk, w_uv;
+    const float *dq_norm = nullptr, *dkv_norm = nullptr;
+    // state-space scan (ScanSpec): input projection; convolution taps [channels, taps] and bias, step bias, log decay rate, skip gain per head,
+    // gain of the grouped output norm (all F32); the sequence's state: last taps - 1 convolution inputs and S [heads, vdim, state] (owned)
+    Weight ssm_in;
+    const float *ssm_conv = nullptr, *ssm_conv_b = nullptr, *ssm_dt_bias = nullptr, *ssm_a_log = nullptr, *ssm_d = nullptr, *ssm_norm = nullptr;
+    float *conv_state = nullptr, *ssm_state = nullptr;
+    // feed-forward biases, the router's choice correction, gate matrices of gated experts (+ their device pointer table)
+    const float *gate_b = nullptr, *up_b = nullptr, *down_b = nullptr, *route_corr = nullptr;
+    std::vector<Weight> e_gate;
+    const void** e_gate_tab = nullptr;
+    // per-layer token input: gate [side_dim, width], projection [width, side_dim], gain [width]
+    Weight side_gate, side_proj;
+    const float* side_norm = nullptr;
 };
 
 class Model {
@@ -129,6 +144,13 @@ private:
     void layer_streams_token(int i, cudaStream_t s);
     void layer_streams_rows(int i, int T, int p0, cudaStream_t s);
     MoeWeights moe_of(int i, bool with_shared) const;
+    // POST_NORM block form (latent attention / state-space scan mixers, biased or routed gated feed-forward, per-layer token input):
+    // T rows at positions base.. (base = *pos_dev when given, else p0); T == 1 with pos_dev is the captured decode step.
+    struct RowBufs { float *x = nullptr, *y = nullptr, *t[5] = {nullptr, nullptr, nullptr, nullptr, nullptr}; };
+    void layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev, int p0, const RowBufs& B, cudaStream_t s);
+    void rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s);      // C = A . W^T: GEMV for one row, else spec_gemm
+    size_t row_scratch_width() const;         // widest intermediate row of any POST_NORM layer
+    void cache_row_widths(int i, size_t& k, size_t& v) const;   // elements per position in layer i's two caches
     int n_streams() const { return cfg_.streams > 0 ? cfg_.streams : 1; }
     bool finalize_spec();
     void step_body_spec(cudaStream_t s);
@@ -150,6 +172,8 @@ private:
     float *moe_wt_ = nullptr, *moe_sgate_ = nullptr, *moe_act_ = nullptr;
     int* moe_offsets_host_ = nullptr;     // pinned: per-expert row offsets of the current prompt chunk (tensor-core expert GEMMs)
     float* ident_tab_ = nullptr;          // {1}: mixing matrix and write gain of a single residual stream
+    Weight side_embd_;                    // second token embedding [vocab, layers * side_dim] (ModelConfig::side_dim)
+    RowBufs dec_;                         // POST_NORM decode step: x is hidden_, the rest one scratch row each (stable addresses for the graph)
     std::vector<int> want_;               // places (indices into the current forward's tokens) whose logits are collected
     float* want_out_ = nullptr;           // device [want_cap_, vocab]
     size_t want_cap_ = 0;
@@ -211,6 +235,7 @@ private:
         float *xs = nullptr, *maps = nullptr;     // STREAMS: the residual streams [T, S, width]; attention maps' outputs [T, heads * maps * vdim]
         int *sel = nullptr, *work = nullptr;      // mixture of experts: chosen experts [T, top]; grouping tables
         float *g2 = nullptr; void *moe_ws = nullptr;   // tensor-core experts: rows gathered in expert order [T*top, width]; per-expert padded split workspace
+        float *gate_rows = nullptr;                    // gated experts: W_gate h of the grouped rows [T*top, ff]
         float *wt = nullptr, *sgate = nullptr, *act_rows = nullptr, *y_rows = nullptr;   // weights [T, top], shared gate [T], grouped rows [T*top, ff | width]
     } pf_;
     // Prompts shorter than this replay token by token through the decode chain (exact-integer GEMVs); longer ones take the batched

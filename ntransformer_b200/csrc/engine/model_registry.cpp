@@ -7,7 +7,7 @@
 namespace nt { namespace b200 {
 
 const std::vector<const ModelFamily*>& model_families() {
-    static const std::vector<const ModelFamily*> all = {zelunex_family(), vebotar_family()};
+    static const std::vector<const ModelFamily*> all = {zelunex_family(), vebotar_family(), tanolorn_family()};
     return all;
 }
 
@@ -15,7 +15,9 @@ bool slot_is_f32_table(TensorSlot s) {
     switch (s) {
         case TensorSlot::EMBED: case TensorSlot::HEAD: case TensorSlot::WQ: case TensorSlot::WK: case TensorSlot::WV: case TensorSlot::WO:
         case TensorSlot::GATE: case TensorSlot::UP: case TensorSlot::DOWN: case TensorSlot::EXPERT_UP: case TensorSlot::EXPERT_DOWN:
-        case TensorSlot::SHARED_UP: case TensorSlot::SHARED_DOWN: return false;
+        case TensorSlot::SHARED_UP: case TensorSlot::SHARED_DOWN: case TensorSlot::EXPERT_GATE:
+        case TensorSlot::W_DQ: case TensorSlot::W_UQ: case TensorSlot::W_DKV: case TensorSlot::W_UK: case TensorSlot::W_UV:
+        case TensorSlot::SSM_IN: case TensorSlot::SIDE_EMBED: case TensorSlot::SIDE_GATE: case TensorSlot::SIDE_PROJ: return false;
         default: return true;
     }
 }

@@ -13,7 +13,11 @@ namespace nt { namespace b200 {
 enum class TensorSlot { EMBED, HEAD, OUT_NORM, NORM1, NORM2, WQ, WK, WV, WO, Q_NORM, K_NORM, GATE, UP, DOWN, LS1, LS2,
                         LQ1, LK1, LQ2, LK2,                         // differential attention: the four vectors of lambda
                         HC1_IN, HC1_OUT, HC1_MIX, HC2_IN, HC2_OUT, HC2_MIX,   // residual streams: read blend, write gains, stream mixing [from, to]
-                        ROUTER, EXPERT_UP, EXPERT_DOWN, SHARED_UP, SHARED_DOWN, SHARED_GATE };
+                        ROUTER, EXPERT_UP, EXPERT_DOWN, SHARED_UP, SHARED_DOWN, SHARED_GATE,
+                        EXPERT_GATE, ROUTE_CORRECTION, GATE_B, UP_B, DOWN_B,              // gated experts, choice correction, feed-forward biases
+                        W_DQ, DQ_NORM, W_UQ, W_DKV, DKV_NORM, W_UK, W_UV,                 // low-rank attention (WO is shared with the other mixers)
+                        SSM_IN, SSM_CONV, SSM_CONV_B, SSM_DT_BIAS, SSM_A_LOG, SSM_D, SSM_NORM,   // state-space scan
+                        SIDE_EMBED, SIDE_GATE, SIDE_PROJ, SIDE_NORM };                    // per-layer token input
 
 struct TensorBinding {
     std::string name;      // in the checkpoint
@@ -38,5 +42,6 @@ bool read_model_dir(const std::string& dir, ModelConfig& cfg, const ModelFamily*
 
 const ModelFamily* zelunex_family();      // engine/zelunex.cpp
 const ModelFamily* vebotar_family();      // engine/vebotar.cpp
+const ModelFamily* tanolorn_family();     // engine/tanolorn.cpp
 
 }}  // namespace nt::b200

@@ -51,6 +51,7 @@ bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int
     if (slot == TensorSlot::EMBED) return W(embd_);
     if (slot == TensorSlot::HEAD) return W(head_);
     if (slot == TensorSlot::OUT_NORM) return V(out_norm_);
+    if (slot == TensorSlot::SIDE_EMBED) return W(side_embd_);
     if (layer < 0 || layer >= cfg_.n_layers) return false;
     LayerWeights& L = layers_[(size_t)layer];
     switch (slot) {
@@ -81,10 +82,31 @@ bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int
         case TensorSlot::SHARED_GATE: return V(L.shared_gate);
         case TensorSlot::SHARED_UP: return W(L.sh_up);
         case TensorSlot::SHARED_DOWN: return W(L.sh_down);
-        case TensorSlot::EXPERT_UP: case TensorSlot::EXPERT_DOWN: {
+        case TensorSlot::W_DQ: return W(L.w_dq);
+        case TensorSlot::W_UQ: return W(L.w_uq);
+        case TensorSlot::W_DKV: return W(L.w_dkv);
+        case TensorSlot::W_UK: return W(L.w_uk);
+        case TensorSlot::W_UV: return W(L.w_uv);
+        case TensorSlot::DQ_NORM: return V(L.dq_norm);
+        case TensorSlot::DKV_NORM: return V(L.dkv_norm);
+        case TensorSlot::SSM_IN: return W(L.ssm_in);
+        case TensorSlot::SSM_CONV: return V(L.ssm_conv);
+        case TensorSlot::SSM_CONV_B: return V(L.ssm_conv_b);
+        case TensorSlot::SSM_DT_BIAS: return V(L.ssm_dt_bias);
+        case TensorSlot::SSM_A_LOG: return V(L.ssm_a_log);
+        case TensorSlot::SSM_D: return V(L.ssm_d);
+        case TensorSlot::SSM_NORM: return V(L.ssm_norm);
+        case TensorSlot::GATE_B: return V(L.gate_b);
+        case TensorSlot::UP_B: return V(L.up_b);
+        case TensorSlot::DOWN_B: return V(L.down_b);
+        case TensorSlot::ROUTE_CORRECTION: return V(L.route_corr);
+        case TensorSlot::SIDE_GATE: return W(L.side_gate);
+        case TensorSlot::SIDE_PROJ: return W(L.side_proj);
+        case TensorSlot::SIDE_NORM: return V(L.side_norm);
+        case TensorSlot::EXPERT_UP: case TensorSlot::EXPERT_DOWN: case TensorSlot::EXPERT_GATE: {
             const int E = cfg_.layers[(size_t)layer].experts;
             if (index < 0 || index >= E) return false;
-            std::vector<Weight>& v = slot == TensorSlot::EXPERT_UP ? L.e_up : L.e_down;
+            std::vector<Weight>& v = slot == TensorSlot::EXPERT_UP ? L.e_up : (slot == TensorSlot::EXPERT_GATE ? L.e_gate : L.e_down);
             if ((int)v.size() != E) v.assign((size_t)E, Weight{});
             return W(v[(size_t)index]);
         }
@@ -164,6 +186,49 @@ bool Model::finalize_spec() {
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerSpec& S = cfg_.layers[(size_t)i];
         const LayerWeights& L = layer_weights(i);
+        if (S.form == BlockForm::POST_NORM) {
+            LayerWeights& M = layers_[(size_t)i];
+            bool ok = L.attn_norm && L.wo.ptr;
+            if (S.mixer == MixerKind::ATTN_LATENT)
+                ok = ok && L.w_dq.ptr && L.dq_norm && L.w_uq.ptr && L.w_uk.ptr && L.w_uv.ptr && (S.kv_from >= 0 || (L.w_dkv.ptr && L.dkv_norm));
+            else if (S.mixer == MixerKind::SSM_SCAN)
+                ok = ok && L.ssm_in.ptr && L.ssm_conv && L.ssm_conv_b && L.ssm_dt_bias && L.ssm_a_log && L.ssm_d && L.ssm_norm;
+            else { fprintf(stderr, "model: layer %d: this mixer has no post-norm kernels\n", i); return false; }
+            if (S.ff > 0 && S.ff_kind == FfKind::GLU) ok = ok && L.ffn_norm && L.gate.ptr && L.up.ptr && L.down.ptr && (!S.ff_bias || (L.gate_b && L.up_b && L.down_b));
+            if (S.ff > 0 && S.ff_kind == FfKind::MOE_GLU) {
+                ok = ok && L.ffn_norm && L.router && (!S.route.correction || L.route_corr) && (int)L.e_up.size() == S.experts && (int)L.e_down.size() == S.experts &&
+                     (int)L.e_gate.size() == S.experts;
+                const DType edt = ok ? L.e_up[0].dtype : DType::F32;
+                for (int e = 0; ok && e < S.experts; e++)
+                    ok = L.e_up[(size_t)e].ptr && L.e_down[(size_t)e].ptr && L.e_gate[(size_t)e].ptr && L.e_up[(size_t)e].dtype == edt && L.e_down[(size_t)e].dtype == edt &&
+                         L.e_gate[(size_t)e].dtype == edt;
+            }
+            if (S.ff > 0 && S.ff_kind == FfKind::MOE_RELU2) { fprintf(stderr, "model: layer %d: this feed-forward has no post-norm kernels\n", i); return false; }
+            if (cfg_.side_dim > 0) ok = ok && side_embd_.ptr && L.side_gate.ptr && L.side_proj.ptr && L.side_norm;
+            if (!ok) { fprintf(stderr, "model: layer %d is missing tensors\n", i); return false; }
+            if (S.mixer == MixerKind::ATTN_LATENT && S.latent.kv_rank > 512) { fprintf(stderr, "model: layer %d: latents wider than 512 are not covered\n", i); return false; }
+            if (S.mixer == MixerKind::SSM_SCAN) {
+                if (S.scan.state > 256) { fprintf(stderr, "model: layer %d: scan states larger than 256 are not covered\n", i); return false; }
+                const size_t ch = (size_t)S.heads * S.vdim + 2 * (size_t)S.scan.groups * S.scan.state;
+                M.conv_state = dmalloc<float>((size_t)std::max(1, S.scan.conv - 1) * ch);
+                M.ssm_state = dmalloc<float>((size_t)S.heads * S.vdim * S.scan.state);
+                NT_CUDA_CHECK(cudaMemset(M.conv_state, 0, sizeof(float) * (size_t)std::max(1, S.scan.conv - 1) * ch));
+                NT_CUDA_CHECK(cudaMemset(M.ssm_state, 0, sizeof(float) * (size_t)S.heads * S.vdim * S.scan.state));
+            }
+            if (S.ff > 0 && S.ff_kind == FfKind::MOE_GLU) {
+                std::vector<const void*> up((size_t)S.experts), down((size_t)S.experts), gate((size_t)S.experts);
+                for (int e = 0; e < S.experts; e++) { up[(size_t)e] = L.e_up[(size_t)e].ptr; down[(size_t)e] = L.e_down[(size_t)e].ptr; gate[(size_t)e] = L.e_gate[(size_t)e].ptr; }
+                M.e_up_tab = dmalloc<const void*>((size_t)S.experts);
+                M.e_down_tab = dmalloc<const void*>((size_t)S.experts);
+                M.e_gate_tab = dmalloc<const void*>((size_t)S.experts);
+                NT_CUDA_CHECK(cudaMemcpy(M.e_up_tab, up.data(), sizeof(void*) * up.size(), cudaMemcpyHostToDevice));
+                NT_CUDA_CHECK(cudaMemcpy(M.e_down_tab, down.data(), sizeof(void*) * down.size(), cudaMemcpyHostToDevice));
+                NT_CUDA_CHECK(cudaMemcpy(M.e_gate_tab, gate.data(), sizeof(void*) * gate.size(), cudaMemcpyHostToDevice));
+                moe_act = std::max(moe_act, S.top * S.ff);
+                topmax = std::max(topmax, S.top);
+            }
+            continue;
+        }
         if (S.form == BlockForm::STREAMS) {
             LayerWeights& M = layers_[(size_t)i];
             const bool kv_ok = S.kv_from >= 0 || (L.wk.ptr && L.wv.ptr);
@@ -212,6 +277,27 @@ bool Model::finalize_spec() {
     }
     cache_dt_ = exact32_ ? DType::F32 : DType::BF16;
     NT_CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    if (cfg_.norm_gain_offset != 0.f) {
+        // gains stored around zero: the offset is added once, into F32 copies the kernels read as plain gains
+        auto fold = [&](const float*& g) {
+            if (!g) return;
+            std::vector<float> h((size_t)hidden);
+            NT_CUDA_CHECK(cudaMemcpy(h.data(), g, sizeof(float) * h.size(), cudaMemcpyDeviceToHost));
+            for (float& v : h) v += cfg_.norm_gain_offset;
+            float* d = dmalloc<float>(h.size());
+            NT_CUDA_CHECK(cudaMemcpy(d, h.data(), sizeof(float) * h.size(), cudaMemcpyHostToDevice));
+            owned_.push_back(d);
+            g = d;
+        };
+        fold(out_norm_);
+        for (LayerWeights& L : layers_) { fold(L.attn_norm); fold(L.ffn_norm); }
+    }
+    if (cfg_.layers[0].form == BlockForm::POST_NORM) {
+        const size_t m1 = row_scratch_width();
+        dec_.y = dmalloc<float>(m1);
+        for (float*& t : dec_.t) t = dmalloc<float>(m1);
+        moe_sel_ = dmalloc<int>(topmax); moe_wt_ = dmalloc<float>(topmax); moe_act_ = dmalloc<float>(moe_act);
+    }
     hidden_ = dmalloc<float>(hidden);
     xnorm_ = dmalloc<float>(hidden);
     q_ = dmalloc<float>(qmax); k_ = dmalloc<float>(kmax); v_ = dmalloc<float>(vmax); attn_ = dmalloc<float>(omax);
@@ -236,7 +322,10 @@ bool Model::finalize_spec() {
     for (int i = 0; i < cfg_.n_layers; i++) {          // every layer RUN owns a cache, also one that borrows its tensors; not one that reads another's rows
         const LayerSpec& S = cfg_.layers[(size_t)i];
         if (S.kv_from >= 0) { kcs_[(size_t)i] = kcs_[(size_t)S.kv_from]; vcs_[(size_t)i] = vcs_[(size_t)S.kv_from]; cache_owned_[(size_t)i] = 0; continue; }
-        const size_t kb = es * max_seq * S.kv_heads * S.maps * S.dim, vb = es * max_seq * S.kv_heads * S.vdim;
+        size_t kw = 0, vw = 0;
+        cache_row_widths(i, kw, vw);
+        if (kw + vw == 0) continue;                        // a mixer without cache rows (state-space scan)
+        const size_t kb = es * max_seq * kw, vb = es * max_seq * vw;
         if (cudaMalloc(&kcs_[(size_t)i], std::max<size_t>(kb, 16)) != cudaSuccess || cudaMalloc(&vcs_[(size_t)i], std::max<size_t>(vb, 16)) != cudaSuccess) {
             cudaGetLastError();
             fprintf(stderr, "model: cannot allocate the KV cache for %d tokens\n", max_seq);
@@ -265,6 +354,12 @@ void Model::step_body_spec(cudaStream_t s) {
     const int* pos_dev = step_dev_ + 1;
     const float m = cfg_.residual_mult;
     embed_rows(hidden_, embd_.ptr, embd_.dtype, step_dev_, 1, hidden, s);
+    if (cfg_.layers[0].form == BlockForm::POST_NORM) {
+        RowBufs B = dec_;
+        B.x = hidden_;
+        for (int i = 0; i < cfg_.n_layers; i++) layer_postnorm(i, 1, step_dev_, pos_dev, 0, B, s);
+        return;
+    }
     if (cfg_.layers[0].form == BlockForm::STREAMS) {
         // the residual lives in streams_ [S, width]; hidden_ holds the embedding row and, at the end, the sum of the streams for the head
         streams_spread(streams_, hidden_, cfg_.embed_scale, 1, n_streams(), hidden, s);
@@ -305,12 +400,18 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream_));
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, (void*)pf_.g, (void*)pf_.u, (void*)pf_.h, (void*)pf_.tmp,
                     pf_.ws, pf_.ws2, pf_.hws, (void*)pf_.tok, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt, (void*)pf_.sgate,
-                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws})
+                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws, (void*)pf_.gate_rows})
         if (p) cudaFree(p);
-    pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = pf_.g2 = nullptr; pf_.sel = pf_.work = nullptr; pf_.moe_ws = nullptr;
+    pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = pf_.g2 = pf_.gate_rows = nullptr; pf_.sel = pf_.work = nullptr; pf_.moe_ws = nullptr;
     const size_t T = (size_t)((tokens + 127) / 128 * 128), hidden = (size_t)cfg_.hidden_size;
     size_t qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1, mapmax = 1, topmax = 0, emax = 1, effmax = 1;
+    const bool post_form = cfg_.layers[0].form == BlockForm::POST_NORM;
     for (const LayerSpec& S : cfg_.layers) {
+        if (post_form) {                  // five scratch rows of the widest intermediate; routed experts as below
+            qmax = kmax = vmax = omax = ffmax = row_scratch_width();
+            if (S.ff_kind == FfKind::MOE_GLU && S.ff > 0) { topmax = std::max(topmax, (size_t)S.top); emax = std::max(emax, (size_t)S.experts); effmax = std::max(effmax, (size_t)S.ff); }
+            continue;
+        }
         qmax = std::max(qmax, (size_t)S.heads * S.maps * S.dim); kmax = std::max(kmax, (size_t)S.kv_heads * S.maps * S.dim); vmax = std::max(vmax, (size_t)S.kv_heads * S.vdim);
         omax = std::max(omax, (size_t)S.heads * S.vdim); mapmax = std::max(mapmax, (size_t)S.heads * S.maps * S.vdim);
         if (S.ff_kind == FfKind::MOE_RELU2 && S.ff > 0) {
@@ -318,9 +419,8 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
             ffmax = std::max(ffmax, std::max((size_t)S.shared_ff, hidden));       // shared expert: activations [T, shared_ff], then its output [T, width]
         } else ffmax = std::max(ffmax, (size_t)S.ff);
     }
-    if (cfg_.layers[0].form == BlockForm::STREAMS) {
-        pf_.xs = dmalloc<float>(T * n_streams() * hidden);
-        pf_.maps = dmalloc<float>(T * mapmax);
+    if (cfg_.layers[0].form == BlockForm::STREAMS || post_form) {
+        if (!post_form) { pf_.xs = dmalloc<float>(T * n_streams() * hidden); pf_.maps = dmalloc<float>(T * mapmax); }
         if (topmax > 0) {
             pf_.sel = dmalloc<int>(T * topmax); pf_.wt = dmalloc<float>(T * topmax); pf_.sgate = dmalloc<float>(T);
             pf_.work = dmalloc<int>(moe_work_ints((int)T, (int)emax, (int)topmax));
@@ -337,10 +437,16 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     pf_.g = dmalloc<float>(T * ffmax); pf_.u = dmalloc<float>(T * ffmax);
     pf_.tok = dmalloc<int>(T);
     pf_.ws = pf_.ws2 = pf_.hws = nullptr;
+    if (post_form && topmax > 0) pf_.gate_rows = dmalloc<float>(T * topmax * effmax);      // the gate half of the gated experts' rows
     bool any_tc = false;
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerWeights& L = layer_weights(i);
-        for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.sh_up, &L.sh_down}) any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
+        for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.sh_up, &L.sh_down, &L.w_dq, &L.w_uq, &L.w_dkv, &L.ssm_in, &L.side_gate, &L.side_proj})
+            any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
+    }
+    if (post_form && any_tc) {            // one split workspace: rows_matmul splits its input right before the GEMM
+        pf_.ws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)std::max(hidden, ffmax)));
+        any_tc = false;
     }
     if (any_tc) {                         // BF16 hi/lo splits of the three GEMM inputs (normed block input, attention output, gated activation)
         pf_.hws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)hidden));
@@ -384,10 +490,13 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
         last_rows = T;
         NT_CUDA_CHECK(cudaMemcpyAsync(pf_.tok, tokens + c0, sizeof(int) * (size_t)T, cudaMemcpyHostToDevice, s));
         embed_rows(pf_.x, embd_.ptr, embd_.dtype, pf_.tok, T, hidden, s);
-        const bool streams_form = cfg_.layers[0].form == BlockForm::STREAMS;
+        const bool streams_form = cfg_.layers[0].form == BlockForm::STREAMS, post_form = cfg_.layers[0].form == BlockForm::POST_NORM;
         if (streams_form) streams_spread(pf_.xs, pf_.x, cfg_.embed_scale, T, n_streams(), hidden, s);
+        RowBufs rb;
+        rb.x = pf_.x; rb.y = pf_.tmp; rb.t[0] = pf_.q; rb.t[1] = pf_.k; rb.t[2] = pf_.v; rb.t[3] = pf_.attn; rb.t[4] = pf_.g;
         for (int i = 0; i < cfg_.n_layers; i++) {
             if (streams_form) { layer_streams_rows(i, T, p0, s); continue; }
+            if (post_form) { layer_postnorm(i, T, pf_.tok, nullptr, p0, rb, s); continue; }
             const LayerSpec& S = cfg_.layers[(size_t)i];
             const LayerWeights& L = layer_weights(i);
             // the block's normed input feeds q, k, v, gate and up: as FP32 rows, as a BF16 split, or both, by what those matrices take
@@ -560,6 +669,115 @@ void Model::layer_streams_rows(int i, int T, int p0, cudaStream_t s) {
     }
     moe_combine(pf_.tmp, pf_.y_rows, pf_.work, pf_.wt, pf_.sgate, shared_y, T, S.experts, S.top, hidden, s);
     streams_write(pf_.xs, pf_.tmp, one ? ident_tab_ : L.hc_mix[1], one ? ident_tab_ : L.hc_out[1], T, NS, hidden, s);
+}
+
+// ---- BlockForm::POST_NORM layers (latent attention, state-space scan, biased / routed gated feed-forward, per-layer token input) ----
+
+void Model::cache_row_widths(int i, size_t& k, size_t& v) const {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    if (S.mixer == MixerKind::SSM_SCAN) { k = v = 0; return; }                                             // a state, no rows
+    if (S.mixer == MixerKind::ATTN_LATENT) { k = (size_t)S.latent.kv_rank + S.latent.rot_dim; v = 0; return; }   // [latent | rotated key part]
+    k = (size_t)S.kv_heads * S.maps * S.dim;
+    v = (size_t)S.kv_heads * S.vdim;
+}
+
+size_t Model::row_scratch_width() const {
+    size_t m = (size_t)cfg_.hidden_size;
+    for (const LayerSpec& S : cfg_.layers) {
+        if (S.mixer == MixerKind::ATTN_LATENT) {
+            const LatentSpec& A = S.latent;
+            m = std::max({m, (size_t)A.q_rank, (size_t)A.kv_rank + A.rot_dim, (size_t)S.heads * (S.dim + A.rot_dim), (size_t)S.heads * (A.kv_rank + A.rot_dim),
+                          (size_t)S.heads * S.vdim});
+        } else if (S.mixer == MixerKind::SSM_SCAN) {
+            const size_t inner = (size_t)S.heads * S.vdim, ch = inner + 2 * (size_t)S.scan.groups * S.scan.state;
+            m = std::max(m, inner + ch + S.heads);
+        }
+        if (S.ff_kind == FfKind::GLU) m = std::max(m, (size_t)S.ff);
+        m = std::max(m, (size_t)cfg_.side_dim);
+    }
+    return m;
+}
+
+// C [T, w.rows] = A [T, w.cols] . W^T.  One row: the GEMV.  More: the tensor-core GEMM from a BF16 split of A made here when the matrix
+// qualifies (never in exact mode), else the FP32 GEMM on CUDA cores.
+void Model::rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s) {
+    if (T == 1) {
+        GemvMat m = mat_of(w, C);
+        gemv_dense(&m, 1, w.cols, A, DENSE_STORE, nullptr, 1.f, s);
+        return;
+    }
+    const bool tc = pf_.ws && spec_tc_ok(w);
+    if (tc) split_activations(pf_.ws, A, T, w.cols, s, true);
+    spec_gemm(C, A, tc ? pf_.ws : nullptr, w, T, DENSE_STORE, nullptr, 1.f, s);
+}
+
+// One layer over T rows: x += norm1(mixer(x)); x += norm2(ff(x)); x += side(x, token).  The sublayers read x itself.
+void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev, int p0, const RowBufs& B, cudaStream_t s) {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    const LayerWeights& L = layer_weights(i);
+    LayerWeights& M = layers_[(size_t)i];
+    const int hidden = cfg_.hidden_size;
+    const float eps = cfg_.norm_eps;
+    if (S.mixer == MixerKind::ATTN_LATENT) {
+        const LatentSpec& A = S.latent;
+        const int row = A.kv_rank + A.rot_dim;
+        float *cq = B.t[0], *dkv = B.t[1], *q = B.t[2], *qa = B.t[3], *ol = B.t[4], *o = B.t[2];
+        rows_matmul(cq, B.x, L.w_dq, T, s);
+        if (S.kv_from < 0) rows_matmul(dkv, B.x, L.w_dkv, T, s);
+        latent_prep(cq, A.q_rank, L.dq_norm, S.kv_from < 0 ? dkv : nullptr, A.kv_rank, A.rot_dim, L.dkv_norm, eps, kcs_[(size_t)i], cache_dt_, S.rot.dims,
+                    S.rot.interleaved, S.rot.base, T, pos_dev, p0, s);
+        rows_matmul(q, cq, L.w_uq, T, s);
+        latent_q_absorb(qa, q, L.w_uk.ptr, L.w_uk.dtype, T, S.heads, S.dim, A.rot_dim, A.kv_rank, S.rot.dims, S.rot.interleaved, S.rot.base, pos_dev, p0, s);
+        WindowAttn a;                       // one key / value head: keys are the whole cache rows, values their first kv_rank numbers
+        a.heads = S.heads; a.kv_heads = 1; a.dim = row; a.vdim = A.kv_rank; a.scale = S.scale; a.k_stride = row; a.v_stride = row;
+        attention_window(ol, qa, kcs_[(size_t)i], kcs_[(size_t)i], cache_dt_, T, pos_dev, p0, cfg_.max_seq_len, a, s);
+        latent_v_up(o, ol, L.w_uv.ptr, L.w_uv.dtype, T, S.heads, S.vdim, A.kv_rank, s);
+        rows_matmul(B.y, o, L.wo, T, s);
+    } else {
+        const ScanSpec& C = S.scan;
+        const int inner = S.heads * S.vdim, ch = inner + 2 * C.groups * C.state, ld = inner + ch + S.heads;
+        float *u = B.t[0], *xbc = B.t[1], *ys = B.t[2], *yg = B.t[3];
+        rows_matmul(u, B.x, L.ssm_in, T, s);                       // [z | x B C | dt]
+        ssm_conv(xbc, u, ld, inner, M.conv_state, L.ssm_conv, L.ssm_conv_b, T, ch, C.conv, pos_dev, p0, s);
+        ssm_scan(ys, xbc, u, ld, inner + ch, M.ssm_state, L.ssm_dt_bias, L.ssm_a_log, L.ssm_d, T, S.heads, S.vdim, C.state, C.groups, pos_dev, p0, s);
+        ssm_gate_norm(yg, ys, u, ld, 0, L.ssm_norm, eps, T, inner, C.norm_groups, s);
+        rows_matmul(B.y, yg, L.wo, T, s);
+    }
+    add_rmsnorm_rows(B.x, B.y, L.attn_norm, nullptr, T, hidden, eps, s);
+    if (S.ff > 0 && S.ff_kind == FfKind::GLU) {
+        float *g = B.t[0], *up = B.t[1];
+        rows_matmul(g, B.x, L.gate, T, s);
+        rows_matmul(up, B.x, L.up, T, s);
+        glu_bias_mul(g, g, up, L.gate_b, L.up_b, T, S.ff, S.act == GluAct::GELU_TANH, s);
+        rows_matmul(B.y, g, L.down, T, s);
+        add_rmsnorm_rows(B.x, B.y, L.ffn_norm, L.down_b, T, hidden, eps, s);
+    } else if (S.ff > 0) {
+        MoeWeights w;
+        w.router = L.router; w.up = L.e_up_tab; w.down = L.e_down_tab; w.gate = L.e_gate_tab; w.dtype = L.e_up[0].dtype;
+        w.experts = S.experts; w.top = S.top; w.ff = S.ff; w.width = hidden;
+        w.sigmoid = S.route.sigmoid; w.correction = S.route.correction ? L.route_corr : nullptr; w.groups = S.route.groups; w.keep = S.route.keep;
+        if (T == 1) {
+            moe_route(moe_sel_, moe_wt_, nullptr, B.x, w, 1, s);
+            moe_expert_up_token(moe_act_, B.x, moe_sel_, w, s);
+            moe_expert_down_token(B.y, moe_act_, moe_sel_, moe_wt_, nullptr, nullptr, w, s);
+        } else {
+            moe_route(pf_.sel, pf_.wt, nullptr, B.x, w, T, s);
+            moe_group(pf_.work, pf_.sel, T, S.experts, S.top, s);
+            moe_expert_gate_rows(pf_.gate_rows, B.x, pf_.work, w, T, s);
+            moe_expert_up_rows(pf_.act_rows, B.x, pf_.work, w, T, s);
+            glu_bias_mul(pf_.act_rows, pf_.gate_rows, pf_.act_rows, nullptr, nullptr, T * S.top, S.ff, false, s);
+            moe_expert_down_rows(pf_.y_rows, pf_.act_rows, pf_.work, w, T, s);
+            moe_combine(B.y, pf_.y_rows, pf_.work, pf_.wt, nullptr, nullptr, T, S.experts, S.top, hidden, s);
+        }
+        add_rmsnorm_rows(B.x, B.y, L.ffn_norm, nullptr, T, hidden, eps, s);
+    }
+    if (cfg_.side_dim > 0) {
+        float* g = B.t[0];
+        rows_matmul(g, B.x, L.side_gate, T, s);
+        side_gate_rows(g, side_embd_.ptr, side_embd_.dtype, cfg_.n_layers * cfg_.side_dim, i * cfg_.side_dim, tok_dev, T, cfg_.side_dim, s);
+        rows_matmul(B.y, g, L.side_proj, T, s);
+        add_rmsnorm_rows(B.x, B.y, L.side_norm, nullptr, T, hidden, eps, s);
+    }
 }
 
 }}  // namespace nt::b200

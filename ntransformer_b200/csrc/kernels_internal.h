@@ -157,6 +157,8 @@ struct WindowAttn {
     int chunk = 0;                     // > 0 (instead of a window): key j visible from i iff j <= i and j / chunk == i / chunk
     int maps = 1;                      // score maps per head: Q rows are [heads][maps][dim], key rows [kv_heads][maps][dim], values [kv_heads][vdim];
                                        // every map is an attention of its own over the head's values; out [tokens, heads*maps*vdim]
+    int k_stride = 0, v_stride = 0;    // elements between consecutive positions' key / value rows; 0: packed (kv_heads*maps*dim, kv_heads*vdim).
+                                       // With strides the two caches may be one buffer (values = a slice of the key rows: latent attention)
 };
 // Q [tokens, heads*dim] at positions base.. (base = *pos_dev when pos_dev is given, else p0); caches [max_seq, kv_heads*dim|vdim] of
 // cache_dt (F32 or BF16) that already hold the rows of these tokens; out [tokens, heads*vdim].
@@ -190,7 +192,8 @@ void streams_spread(float* X, const float* e, float scale, int tokens, int S, in
 void streams_read(float* u, const float* X, const float* a, int tokens, int S, int width, cudaStream_t s);
 void streams_write(float* X, const float* y, const float* M, const float* b, int tokens, int S, int width, cudaStream_t s);
 void scale_rows(float* x, float scale, size_t n, cudaStream_t s);
-// Mixture of squared-ReLU experts.  h [tokens, width] F32 (already normed).
+// Mixture of experts.  h [tokens, width] F32 (already normed where the block norms).  Squared-ReLU experts W_down relu(W_up h)^2, or —
+// `gate` given — gated experts W_down (silu(W_gate h) * W_up h).
 struct MoeWeights {
     const float* router = nullptr;       // [experts, width] F32
     const float* shared_gate = nullptr;  // [width] F32 or null
@@ -200,6 +203,13 @@ struct MoeWeights {
     const void* shared_down = nullptr;   //   run the shared expert as one more slot
     DType dtype = DType::BF16;           // of the expert matrices
     int experts = 0, top = 0, ff = 0, width = 0, shared_ff = 0;
+    const void* const* gate = nullptr;   // device table [experts] of [ff, width] rows: the experts are gated units
+    // How the router chooses and weights (engine/layer_spec.h RouteSpec).  sigmoid: score = sigmoid(logit), weight = the chosen experts'
+    // scores as they are; else softmax over the chosen logits.  correction [experts]: added to the scores for the choice only.
+    // groups > 0: only experts of the `keep` runs of neighbours with the largest sum of their two largest choice scores can be chosen.
+    bool sigmoid = false;
+    const float* correction = nullptr;
+    int groups = 0, keep = 0;
 };
 // Router: logits in F32, the `top` largest (lowest index on ties), softmax over the chosen -> sel [tokens, top], wt [tokens, top];
 // sgate [tokens] = sigmoid(<shared_gate, h>) when shared_gate is given.
@@ -216,7 +226,9 @@ void moe_expert_down_token(float* y, const float* act, const int* sel, const flo
 //   work: ints [experts + 1 (offsets) + tokens*top (row -> token) + tokens*top (assignment -> row)]
 size_t moe_work_ints(int tokens, int experts, int top);
 void moe_group(int* work, const int* sel, int tokens, int experts, int top, cudaStream_t s);
-void moe_expert_up_rows(float* act_rows, const float* h, const int* work, const MoeWeights& w, int tokens, cudaStream_t s);     // [tokens*top, ff]
+// [tokens*top, ff]: relu(W_up h)^2, or for gated experts the plain W_up h; moe_expert_gate_rows: W_gate h (combine with glu_bias_mul)
+void moe_expert_up_rows(float* act_rows, const float* h, const int* work, const MoeWeights& w, int tokens, cudaStream_t s);
+void moe_expert_gate_rows(float* gate_rows, const float* h, const int* work, const MoeWeights& w, int tokens, cudaStream_t s);
 void moe_expert_down_rows(float* y_rows, const float* act_rows, const int* work, const MoeWeights& w, int tokens, cudaStream_t s); // [tokens*top, width]
 // y [tokens, width] = sum_k wt[t, k] * y_rows[row(t, k)] (+ sgate[t] * shared_y[t])
 void moe_combine(float* y, const float* y_rows, const int* work, const float* wt, const float* sgate, const float* shared_y, int tokens,
@@ -224,6 +236,29 @@ void moe_combine(float* y, const float* y_rows, const int* work, const float* wt
 // h rows in the grouped order (the tensor-core path splits them per expert): out [tokens*top, width]
 void moe_gather_rows(float* out, const float* h, const int* work, int tokens, int experts, int top, int width, cudaStream_t s);
 void relu2(float* x, size_t n, cudaStream_t s);
+
+// ---- attention_latent.cu / ssm_scan.cu / postnorm.cu: mechanisms added with the third layer-spec family ----
+// Latent attention (engine/layer_spec.h LatentSpec).  cq [T, q_rank]: RMS-normed in place (gain).  dkv [T, kv_rank + rot_dim] (null: the layer
+// reads another layer's rows): [RMS-normed first part | rotated rest] -> cache row base + t of `cache` ([max_seq, kv_rank + rot_dim]).
+void latent_prep(float* cq, int q_rank, const float* q_gain, const float* dkv, int kv_rank, int rot_dim, const float* kv_gain, float eps, void* cache,
+                 DType cache_dt, int rot_dims, bool interleaved, float rot_base, int T, const int* pos_dev, int p0, cudaStream_t s);
+// q [T, heads, dim + rot_dim] -> qa [T, heads, kv_rank + rot_dim] = [W_uk,h^T q_unrotated | rot(q_rotated)];  W_uk [heads * dim, kv_rank]
+void latent_q_absorb(float* qa, const float* q, const void* W_uk, DType dt, int T, int heads, int dim, int rot_dim, int kv_rank, int rot_dims,
+                     bool interleaved, float rot_base, const int* pos_dev, int p0, cudaStream_t s);
+// ol [T, heads, kv_rank] -> out [T, heads * vdim] = W_uv,h ol_h;  W_uv [heads * vdim, kv_rank]
+void latent_v_up(float* out, const float* ol, const void* W_uv, DType dt, int T, int heads, int vdim, int kv_rank, cudaStream_t s);
+// State-space scan (ScanSpec).  u [T, ld]: the input projection's rows; channels of interest start at a column offset.
+// conv_state [taps - 1, ch], state [heads, vdim, N]: the sequence's state, read unless the step starts at position 0, updated in place.
+void ssm_conv(float* out, const float* u, int ld, int col0, float* conv_state, const float* w, const float* b, int T, int ch, int taps,
+              const int* pos_dev, int p0, cudaStream_t s);
+void ssm_scan(float* y, const float* xbc, const float* u, int ld, int dt_col0, float* state, const float* dt_bias, const float* A_log, const float* D,
+              int T, int heads, int vdim, int N, int groups, const int* pos_dev, int p0, cudaStream_t s);
+void ssm_gate_norm(float* out, const float* y, const float* u, int ld, int z_col0, const float* gain, float eps, int T, int inner, int norm_groups,
+                   cudaStream_t s);
+// Post-norm block form: x[t] += rms(y[t] + bias) * gain;  out = act(gate + b_g) * (up + b_u);  g[t, j] <- gelu_tanh(g[t, j]) * E[token_t, col0 + j]
+void add_rmsnorm_rows(float* x, const float* y, const float* gain, const float* bias, int rows, int width, float eps, cudaStream_t s);
+void glu_bias_mul(float* out, const float* gate, const float* up, const float* gate_bias, const float* up_bias, int rows, int cols, bool gelu, cudaStream_t s);
+void side_gate_rows(float* g, const void* E, DType dt, int e_cols, int col0, const int* tokens_dev, int rows, int dim, cudaStream_t s);
 
 // Programmatic dependent launch (PDL): when enabled, kernels are launched with
 // cudaLaunchAttributeProgrammaticStreamSerialization so that a kernel's prologue (barrier init, TMA weight

@@ -8,6 +8,9 @@
 //                            GEMMs (64x64x16 tiles, FP32 FMA on CUDA cores) run every expert over its own rows only, and moe_combine
 //                            sums a token's rows in k order.  Every output element is one dot product in a fixed order, so a token's
 //                            result does not depend on which other tokens share its tile.
+// Variants (MoeWeights): gated experts W_down (silu(W_gate h) * W_up h) through a third pointer table; a router that scores by
+// sigmoid, adds a correction vector for the choice only, restricts the choice to the best runs of neighbouring experts and weights
+// by the plain scores.
 // Expert matrices: F32, F16 or BF16 rows.  Compiled WITHOUT --use_fast_math.
 #include "kernels_internal.h"
 #include "ring.cuh"
@@ -92,9 +95,10 @@ constexpr int MAX_EXPERTS = 256;
 __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(int* __restrict__ sel, float* __restrict__ wt, float* __restrict__ sgate,
                                                                   const float* __restrict__ h, const float* __restrict__ router,
                                                                   const float* __restrict__ shared_gate, int experts, int top, int width,
-                                                                  StreamsIO sio, const float* __restrict__ norm_w, float eps, float* __restrict__ h_out) {
+                                                                  int sigmoid, const float* __restrict__ correction, int groups, int keep, StreamsIO sio, const float* __restrict__ norm_w, float eps, float* __restrict__ h_out) {
     extern __shared__ __align__(16) float hs[];
     __shared__ float z[MAX_EXPERTS + 1];
+    __shared__ float sc[MAX_EXPERTS];
     __shared__ float red[RT_WARPS];
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -132,6 +136,40 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(int* __restric
     __syncthreads();
     if (threadIdx.x != 0) return;
     if (shared_gate) sgate[t] = 1.0f / (1.0f + expf(-z[experts]));
+    if (sigmoid) {
+        // scores sigmoid(logit); the choice looks at score + correction, the weight is the plain score of what was chosen
+        for (int e = 0; e < experts; e++) { sc[e] = 1.0f / (1.0f + expf(-z[e])); z[e] = sc[e] + (correction ? correction[e] : 0.f); }
+        if (groups > 0) {
+            // a run of neighbours scores the sum of its two largest choice scores; runs outside the best `keep` drop out (-inf, not 0:
+            // choice scores may be negative); the kept runs are a bit mask
+            const int per = experts / groups;
+            unsigned long long kept[4] = {0ull, 0ull, 0ull, 0ull};
+            for (int k = 0; k < keep; k++) {
+                int bg = -1;
+                float bs = -INFINITY;
+                for (int g = 0; g < groups; g++) {
+                    if (kept[g >> 6] >> (g & 63) & 1ull) continue;
+                    float m1 = -INFINITY, m2 = -INFINITY;
+                    for (int e = g * per; e < (g + 1) * per; e++) { const float v = z[e]; if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) m2 = v; }
+                    const float gs = per >= 2 ? m1 + m2 : m1;
+                    if (bg < 0 || gs > bs) { bs = gs; bg = g; }
+                }
+                kept[bg >> 6] |= 1ull << (bg & 63);
+            }
+            for (int g = 0; g < groups; g++)
+                if (!(kept[g >> 6] >> (g & 63) & 1ull)) for (int e = g * per; e < (g + 1) * per; e++) z[e] = -INFINITY;
+        }
+        for (int k = 0; k < top; k++) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < experts; e++) if (z[e] > bv) { bv = z[e]; best = e; }      // strict: the lowest index wins a tie
+            if (best < 0) best = 0;
+            sel[(size_t)t * top + k] = best;
+            wt[(size_t)t * top + k] = sc[best];
+            z[best] = -INFINITY;
+        }
+        return;
+    }
     // the `top` largest logits, largest first; an expert already taken is marked by -inf
     float zmax = 0.f, den = 0.f;
     for (int k = 0; k < top; k++) {
@@ -149,6 +187,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(int* __restric
 }
 
 struct MoeDev {
+    const void* const* gate;       // null: squared-ReLU experts
     const void* const* up; const void* const* down;
     const void* shared_up; const void* shared_down;
     int top, ff, width, shared_ff;
@@ -174,6 +213,12 @@ __global__ void __launch_bounds__(TK_WARPS * 32) moe_up_token_kernel(float* __re
         else { base = static_cast<const unsigned char*>(m.shared_up); row = r - m.top * m.ff; }
         const unsigned char* wr = base + (size_t)row * pitch;
         const float d = warp_dot<T>(wr, hs, m.width, lane, kvec && (reinterpret_cast<uintptr_t>(wr) & 15) == 0);
+        if (m.gate && r < m.top * m.ff) {       // gated unit: silu(<gate row, h>) * <up row, h>
+            const unsigned char* gr = static_cast<const unsigned char*>(m.gate[sel[r / m.ff]]) + (size_t)row * pitch;
+            const float g = warp_dot<T>(gr, hs, m.width, lane, kvec && (reinterpret_cast<uintptr_t>(gr) & 15) == 0);
+            if (lane == 0) act[r] = g / (1.0f + expf(-g)) * d;
+            continue;
+        }
         if (lane == 0) { const float z = fmaxf(d, 0.f); act[r] = z * z; }
     }
 }
@@ -353,7 +398,7 @@ __global__ void relu2_kernel(float* __restrict__ x, size_t n) {
     if (i < n) { const float z = fmaxf(x[i], 0.f); x[i] = z * z; }
 }
 
-MoeDev dev_of(const MoeWeights& w) { return MoeDev{w.up, w.down, w.shared_up, w.shared_down, w.top, w.ff, w.width, w.shared_up ? w.shared_ff : 0}; }
+MoeDev dev_of(const MoeWeights& w) { return MoeDev{w.gate, w.up, w.down, w.shared_up, w.shared_down, w.top, w.ff, w.width, w.shared_up ? w.shared_ff : 0}; }
 
 }  // namespace
 
@@ -361,12 +406,15 @@ void moe_route(int* sel, float* wt, float* sgate, const float* h, const MoeWeigh
                const float* norm_w, float eps, float* h_out) {
     const StreamsIO sio = sio_p ? *sio_p : StreamsIO();
     NT_CHECK(w.experts >= 1 && w.experts <= MAX_EXPERTS && w.top >= 1 && w.top <= w.experts, "moe_route: 1 <= top <= experts <= 256");
+    NT_CHECK(w.groups == 0 || (w.sigmoid && w.experts % w.groups == 0 && w.keep >= 1 && w.keep <= w.groups && w.keep * (w.experts / w.groups) >= w.top),
+             "moe_route: expert groups must be equal runs whose kept part holds at least top experts");
     if (tokens <= 0) return;
     const size_t smem = (size_t)w.width * sizeof(float);
     NT_CHECK(smem <= 160 * 1024, "moe_route: the activation row does not fit in shared memory");
     static unsigned long long done = 0;
     if (smem > 40 * 1024) opt_in_dynamic_smem(moe_route_kernel, 160 * 1024, done);
-    launch_k(moe_route_kernel, dim3(tokens), dim3(RT_WARPS * 32), smem, s, sel, wt, sgate, h, w.router, w.shared_gate, w.experts, w.top, w.width, sio, norm_w, eps, h_out);
+    launch_k(moe_route_kernel, dim3(tokens), dim3(RT_WARPS * 32), smem, s, sel, wt, sgate, h, w.router, w.shared_gate, w.experts, w.top, w.width,
+             w.sigmoid ? 1 : 0, w.correction, w.groups, w.keep, sio, norm_w, eps, h_out);
     count_launch();
 }
 
@@ -413,7 +461,17 @@ void moe_group(int* work, const int* sel, int tokens, int experts, int top, cuda
 void moe_expert_up_rows(float* act_rows, const float* h, const int* work, const MoeWeights& w, int tokens, cudaStream_t s) {
     if (tokens <= 0) return;
     const dim3 grid((w.ff + GT - 1) / GT, (tokens + GT - 1) / GT, w.experts);
-#define NT_CALL(TY) launch_k(moe_rows_gemm_kernel<TY>, grid, dim3(256), 0, s, act_rows, h, work + w.experts + 1, w.up, work, w.ff, w.width, 1);
+    const int relu2 = w.gate ? 0 : 1;
+#define NT_CALL(TY) launch_k(moe_rows_gemm_kernel<TY>, grid, dim3(256), 0, s, act_rows, h, work + w.experts + 1, w.up, work, w.ff, w.width, relu2);
+    NT_MOE_DT(NT_CALL)
+#undef NT_CALL
+    count_launch();
+}
+void moe_expert_gate_rows(float* gate_rows, const float* h, const int* work, const MoeWeights& w, int tokens, cudaStream_t s) {
+    if (tokens <= 0) return;
+    NT_CHECK(w.gate != nullptr, "moe_expert_gate_rows: the experts have no gate matrices");
+    const dim3 grid((w.ff + GT - 1) / GT, (tokens + GT - 1) / GT, w.experts);
+#define NT_CALL(TY) launch_k(moe_rows_gemm_kernel<TY>, grid, dim3(256), 0, s, gate_rows, h, work + w.experts + 1, w.gate, work, w.ff, w.width, 0);
     NT_MOE_DT(NT_CALL)
 #undef NT_CALL
     count_launch();
