@@ -823,6 +823,76 @@ def run_family_compare_vebotar(args):
                       "dtype": "bf16 weights, f32 activations", "data": "synthetic", "rows": rows}))
 
 
+TANOLORN_SIZES = {
+    # name: (width, attention heads, unrotated dim, rotated dim, value dim, query rank, key/value rank, scan heads, scan head width, state, experts, top, expert ff).
+    # 4 layers: scan + dense ff, latent attention + experts, scan + experts, latent attention reading layer 1's rows + experts.
+    # The Vebotar model beside it has the same width, attention heads, experts and top; its experts are ungated (2 matrices), so their ff is
+    # 3/2 of ours: equal weights per token.
+    "2048_e8x1536": (2048, 16, 64, 32, 64, 768, 256, 32, 64, 64, 8, 2, 1536),
+    "4096_e16x1536": (4096, 32, 128, 64, 128, 1536, 512, 64, 64, 128, 16, 4, 1536),
+}
+
+
+def run_family_compare_tanolorn(args):
+    """--family-compare --family tanolorn: prompt-pass and decode throughput of the Tanolorn family (BF16 weights; latent attention and
+    state-space scan layers, post-norm, gated experts with grouped sigmoid routing, per-layer token input) beside the closest existing
+    family (Vebotar: BF16 weights, routed experts, shared caches) at equal width, heads and active expert weights.  Device-timed with CUDA
+    events on the model's stream; prompts differ between steps and the weights of either model exceed L2."""
+    import torch
+    from ntransformer_b200 import kernels as K
+    from ntransformer_b200.engine import Model
+    from ntransformer_b200.model_spec import tanolorn_config, tanolorn_random_tensors, vebotar_config, vebotar_random_tensors
+
+    torch.cuda.set_device(0)
+    n_layers, vocab, prompt_len, max_seq = 4, 32000, 2048, 4096
+    hbm, hbm_src = measured_peak_hbm()
+    rows = []
+    for name, (width, heads, dim, rot, vdim, qr, kvr, sh, sv, state, experts, top, eff) in TANOLORN_SIZES.items():
+        tc = tanolorn_config(vocab=vocab, width=width, pattern=("mamba2", "latent_attention", "mamba2", "latent_attention"), kv_from={3: 1},
+                             mlp=("dense", "moe", "moe", "moe"), heads=heads, dim=dim, rot_dim=rot, vdim=vdim, q_rank=qr, kv_rank=kvr, s_heads=sh, s_vdim=sv,
+                             state=state, groups=8, norm_groups=8, ff=2 * width, experts=experts, top=top, eff=eff, route_groups=(4, 2), side=256)
+        vc = vebotar_config(vocab=vocab, width=width, n_layers=n_layers, heads=heads, kv_heads=heads // 4, dim=vdim // 2, vdim=vdim, chunk=max_seq, rot_dims=vdim // 4,
+                            experts=experts, top=top, ff=eff * 3 // 2 // 128 * 128, shared_ff=0, streams=0, kv_from={n_layers - 1: n_layers - 2})
+        row = {"size": name, "layers": n_layers, "prompt_tokens": prompt_len, "decode_context": prompt_len}
+        for label, make in (("tanolorn_bf16", lambda: Model.from_config_json(tc, tanolorn_random_tensors(tc), max_context=max_seq)),
+                            ("vebotar_bf16", lambda: Model.from_config_json(vc, vebotar_random_tensors(vc), max_context=max_seq))):
+            model = make()
+            stream = torch.cuda.ExternalStream(model.stream)
+            prompts = [[token_at(i + 97 * j, vocab) for i in range(prompt_len)] for j in range(4)]
+            for i in range(args.warmup):
+                model.forward_async(prompts[i % 4], 0)
+            model.sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n0 = K.launch_count()
+            psteps = max(3, min(args.steps, 8))
+            a.record(stream)
+            for i in range(psteps):
+                model.forward_async(prompts[i % 4], 0)
+            b.record(stream)
+            model.sync()
+            prefill = psteps * prompt_len / (a.elapsed_time(b) / 1e3)
+            dsteps = max(8, min(args.steps, 256))
+            for i in range(args.warmup):
+                model.forward_async([token_at(i, vocab)], prompt_len + i)
+            model.sync()
+            a.record(stream)
+            for i in range(dsteps):
+                model.forward_async([token_at(i + 5, vocab)], prompt_len + args.warmup + i)
+            b.record(stream)
+            model.sync()
+            ms = a.elapsed_time(b) / dsteps
+            bpt = model.bytes_per_token(prompt_len + args.warmup + dsteps // 2)
+            row[label] = {"prefill_tok_s": round(prefill, 1), "decode_tok_s": round(1e3 / ms, 1), "decode_ms": round(ms, 4),
+                          "decode_bytes_per_token": bpt, "decode_frac_of_hbm_peak": round(bpt / (ms * 1e-3) / (hbm * 1e9), 3),
+                          "launches": int(K.launch_count() - n0)}
+            model.close()
+            del model
+            torch.cuda.empty_cache()
+        rows.append(row)
+    print(json.dumps({"metric": "family_compare", "family": "tanolorn", "unit": "tok/s", "hbm_peak_gbs": hbm, "hbm_peak_source": hbm_src,
+                      "dtype": "bf16 weights, f32 activations", "data": "synthetic", "rows": rows}))
+
+
 def run_family_compare(args):
     """--family-compare: prompt-pass and decode throughput of the Zelunex family (BF16 weights, windowed attention) beside the
     closest GGUF family member (Llama block, F16 weights, full causal attention) at equal layer sizes.  Device-timed with CUDA
@@ -899,8 +969,8 @@ def main():
     ap.add_argument("--all-errs", action="store_true", help="--check only: list the error of every step, not the first 8")
     ap.add_argument("--family-compare", action="store_true",
                     help="instead of the workload: Zelunex beside the Llama block at equal layer sizes, prompt pass and decode (1 GPU)")
-    ap.add_argument("--family", default="zelunex", choices=["zelunex", "vebotar"],
-                    help="--family-compare only: zelunex beside the Llama block (default), or vebotar beside zelunex")
+    ap.add_argument("--family", default="zelunex", choices=["zelunex", "vebotar", "tanolorn"],
+                    help="--family-compare only: zelunex beside the Llama block (default), vebotar beside zelunex, or tanolorn beside vebotar")
     ap.add_argument("--per-token-prompt", action="store_true", help="--check only: our engine replays the prompt token by token like the reference")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -910,7 +980,7 @@ def main():
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     if args.family_compare:
         if rank == 0:
-            (run_family_compare_vebotar if args.family == "vebotar" else run_family_compare)(args)
+            {"vebotar": run_family_compare_vebotar, "tanolorn": run_family_compare_tanolorn}.get(args.family, run_family_compare)(args)
     elif args.check:
         run_check(args, rank, world)
     elif args.impl == "reference":

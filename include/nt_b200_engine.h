@@ -76,6 +76,31 @@ void nt_b200_moe_experts(float* y, const float* h, const int* sel, const float* 
                          const void* shared_up, const void* shared_down, const float* shared_y, int dtype, int experts, int top, int ff, int width,
                          int shared_ff, int tokens, int mode, void* scratch, void* stream);
 
+/* latent attention: cache rows [normed latent : kv_rank | rotated key part : rot_dim]; the query side absorbs the per-head key up-projection */
+void nt_b200_latent_prep(float* cq, int q_rank, const float* q_gain, const float* dkv, int kv_rank, int rot_dim, const float* kv_gain, float eps, void* cache,
+                         int cache_dtype, int rot_dims, int interleaved, float rot_base, int tokens, int p0, void* stream);
+void nt_b200_latent_q_absorb(float* qa, const float* q, const void* W_uk, int dtype, int tokens, int heads, int dim, int rot_dim, int kv_rank, int rot_dims,
+                             int interleaved, float rot_base, int p0, void* stream);
+void nt_b200_latent_v_up(float* out, const float* ol, const void* W_uv, int dtype, int tokens, int heads, int vdim, int kv_rank, void* stream);
+/* full causal attention over ONE key / value head stored as rows of `row` numbers: keys the first dim, values the first vdim of a row */
+void nt_b200_attention_rows(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,
+                            int max_seq, void* stream);
+/* state-space scan: causal convolution + SiLU with a carried state, the recurrence with a carried state, gate + grouped RMS norm */
+void nt_b200_ssm_conv(float* out, const float* u, int ld, int col0, float* conv_state, const float* w, const float* b, int tokens, int ch, int taps, int p0, void* stream);
+void nt_b200_ssm_scan(float* y, const float* xbc, const float* u, int ld, int dt_col0, float* state, const float* dt_bias, const float* A_log, const float* D,
+                      int tokens, int heads, int vdim, int N, int groups, int p0, void* stream);
+void nt_b200_ssm_gate_norm(float* out, const float* y, const float* u, int ld, int z_col0, const float* gain, float eps, int tokens, int inner, int norm_groups,
+                           void* stream);
+/* post-norm block: x += rms(y + bias) * gain; out = act(gate + b_g) * (up + b_u); g <- gelu_tanh(g) * E[token, col0 + j] */
+void nt_b200_add_rmsnorm_rows(float* x, const float* y, const float* gain, const float* bias, int rows, int width, float eps, void* stream);
+void nt_b200_glu_bias_mul(float* out, const float* gate, const float* up, const float* gate_bias, const float* up_bias, int rows, int cols, int gelu, void* stream);
+void nt_b200_side_gate_rows(float* g, const void* E, int dtype, int e_cols, int col0, const int* tokens_dev, int rows, int dim, void* stream);
+/* router with sigmoid scores, a choice-only correction and a limit to the best runs of neighbouring experts; gated experts */
+void nt_b200_moe_route_scored(int* sel, float* wt, const float* h, const float* router, const float* correction, int experts, int top, int groups, int keep,
+                              int width, int tokens, void* stream);
+void nt_b200_moe_glu_experts(float* y, const float* h, const int* sel, const float* wt, const void* const* gate_tab, const void* const* up_tab,
+                             const void* const* down_tab, int dtype, int experts, int top, int ff, int width, int tokens, int mode, void* scratch, void* stream);
+
 /* forward(tokens[seq_len], start_pos): logits of the last token. logits_host may be NULL.  Returns 0. */
 int  nt_model_forward(nt_model_t m, const int* tokens_host, int seq_len, int start_pos, float* logits_host);
 /* asynchronous launch only (no sync, no copy); nt_model_sync waits for the model's stream */

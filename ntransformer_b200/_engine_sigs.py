@@ -72,6 +72,18 @@ ENGINE_SIGNATURES = {
     "nt_b200_streams_write": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "nt_b200_moe_route": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "nt_b200_moe_experts": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "nt_b200_latent_prep": (None, [_vp, _i, _vp, _vp, _i, _i, _vp, _f, _vp, _i, _i, _i, _f, _i, _i, _vp]),
+    "nt_b200_latent_q_absorb": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "nt_b200_latent_v_up": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "nt_b200_attention_rows": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "nt_b200_ssm_conv": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "nt_b200_ssm_scan": (None, [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nt_b200_ssm_gate_norm": (None, [_vp, _vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _vp]),
+    "nt_b200_add_rmsnorm_rows": (None, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "nt_b200_glu_bias_mul": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "nt_b200_side_gate_rows": (None, [_vp, _vp, _i, _i, _i, _vp, _i, _i, _vp]),
+    "nt_b200_moe_route_scored": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nt_b200_moe_glu_experts": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "nt_tp_unique_id": (_i, [_vp]),
     "nt_tp_init": (_i, [_vp, _vp, _i, _i]),
 }

@@ -101,6 +101,17 @@ int nt_model_dir_describe(const char* dir, char* out, size_t cap) {
             text += " chunk=" + std::to_string(L.chunk) + " maps=" + std::to_string(L.maps) + " rot=" + std::to_string(L.rot.dims) + " kv_from=" + std::to_string(L.kv_from) +
                     " experts=" + std::to_string(L.experts) + " top=" + std::to_string(L.top) + " shared_ff=" + std::to_string(L.shared_ff) +
                     " streams=" + std::to_string(cfg.streams);
+        if (L.form == BlockForm::POST_NORM) {
+            text += std::string(" mixer=") + (L.mixer == MixerKind::ATTN_LATENT ? "latent" : "scan");
+            if (L.mixer == MixerKind::ATTN_LATENT)
+                text += " q_rank=" + std::to_string(L.latent.q_rank) + " kv_rank=" + std::to_string(L.latent.kv_rank) + " rot_dim=" + std::to_string(L.latent.rot_dim) +
+                        " rot=" + std::to_string(L.rot.dims) + " kv_from=" + std::to_string(L.kv_from);
+            else
+                text += " state=" + std::to_string(L.scan.state) + " groups=" + std::to_string(L.scan.groups) + " conv=" + std::to_string(L.scan.conv) +
+                        " norm_groups=" + std::to_string(L.scan.norm_groups);
+            text += std::string(" ff_kind=") + (L.ff == 0 ? "none" : L.ff_kind == FfKind::GLU ? "dense" : "moe") + " experts=" + std::to_string(L.experts) + " top=" +
+                    std::to_string(L.top) + " route_groups=" + std::to_string(L.route.groups) + "/" + std::to_string(L.route.keep) + " side=" + std::to_string(cfg.side_dim);
+        }
         text += "\n";
     }
     size_t n = 0;
@@ -212,6 +223,79 @@ void nt_b200_moe_experts(float* y, const float* h, const int* sel, const float* 
     moe_expert_up_rows(act_rows, h, work, w, tokens, s);
     moe_expert_down_rows(y_rows, act_rows, work, w, tokens, s);
     moe_combine(y, y_rows, work, wt, sgate, shared_y, tokens, experts, top, width, s);
+}
+// ---- kernel entries of the mechanisms added with the Tanolorn family (numerics tests) ----
+void nt_b200_latent_prep(float* cq, int q_rank, const float* q_gain, const float* dkv, int kv_rank, int rot_dim, const float* kv_gain, float eps, void* cache,
+                         int cache_dtype, int rot_dims, int interleaved, float rot_base, int tokens, int p0, void* stream) {
+    latent_prep(cq, q_rank, q_gain, dkv, kv_rank, rot_dim, kv_gain, eps, cache, (nt::DType)cache_dtype, rot_dims, interleaved != 0, rot_base, tokens, nullptr, p0,
+                static_cast<cudaStream_t>(stream));
+}
+void nt_b200_latent_q_absorb(float* qa, const float* q, const void* W_uk, int dtype, int tokens, int heads, int dim, int rot_dim, int kv_rank, int rot_dims,
+                             int interleaved, float rot_base, int p0, void* stream) {
+    latent_q_absorb(qa, q, W_uk, (nt::DType)dtype, tokens, heads, dim, rot_dim, kv_rank, rot_dims, interleaved != 0, rot_base, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_latent_v_up(float* out, const float* ol, const void* W_uv, int dtype, int tokens, int heads, int vdim, int kv_rank, void* stream) {
+    latent_v_up(out, ol, W_uv, (nt::DType)dtype, tokens, heads, vdim, kv_rank, static_cast<cudaStream_t>(stream));
+}
+// Full causal attention of `heads` query heads over ONE key / value head whose rows live in `cache` with `row` numbers per position:
+// keys are the first `dim` numbers of a row, values its first `vdim` (the latent-attention layout: dim = row, vdim = kv_rank).
+void nt_b200_attention_rows(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,
+                            int max_seq, void* stream) {
+    WindowAttn a;
+    a.heads = heads; a.kv_heads = 1; a.dim = dim; a.vdim = vdim; a.scale = scale; a.k_stride = row; a.v_stride = row;
+    attention_window(out, Q, cache, cache, (nt::DType)cache_dtype, tokens, nullptr, p0, max_seq, a, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_ssm_conv(float* out, const float* u, int ld, int col0, float* conv_state, const float* w, const float* b, int tokens, int ch, int taps, int p0, void* stream) {
+    ssm_conv(out, u, ld, col0, conv_state, w, b, tokens, ch, taps, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_ssm_scan(float* y, const float* xbc, const float* u, int ld, int dt_col0, float* state, const float* dt_bias, const float* A_log, const float* D,
+                      int tokens, int heads, int vdim, int N, int groups, int p0, void* stream) {
+    ssm_scan(y, xbc, u, ld, dt_col0, state, dt_bias, A_log, D, tokens, heads, vdim, N, groups, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_ssm_gate_norm(float* out, const float* y, const float* u, int ld, int z_col0, const float* gain, float eps, int tokens, int inner, int norm_groups,
+                           void* stream) {
+    ssm_gate_norm(out, y, u, ld, z_col0, gain, eps, tokens, inner, norm_groups, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_add_rmsnorm_rows(float* x, const float* y, const float* gain, const float* bias, int rows, int width, float eps, void* stream) {
+    add_rmsnorm_rows(x, y, gain, bias, rows, width, eps, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_glu_bias_mul(float* out, const float* gate, const float* up, const float* gate_bias, const float* up_bias, int rows, int cols, int gelu, void* stream) {
+    glu_bias_mul(out, gate, up, gate_bias, up_bias, rows, cols, gelu != 0, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_side_gate_rows(float* g, const void* E, int dtype, int e_cols, int col0, const int* tokens_dev, int rows, int dim, void* stream) {
+    side_gate_rows(g, E, (nt::DType)dtype, e_cols, col0, tokens_dev, rows, dim, static_cast<cudaStream_t>(stream));
+}
+// Router with sigmoid scores, a choice-only correction (may be null) and a limit to the best `keep` of `groups` runs of neighbours (groups 0: none)
+void nt_b200_moe_route_scored(int* sel, float* wt, const float* h, const float* router, const float* correction, int experts, int top, int groups, int keep,
+                              int width, int tokens, void* stream) {
+    MoeWeights w;
+    w.router = router; w.experts = experts; w.top = top; w.width = width; w.sigmoid = true; w.correction = correction; w.groups = groups; w.keep = keep;
+    moe_route(sel, wt, nullptr, h, w, tokens, static_cast<cudaStream_t>(stream));
+}
+// Gated experts.  mode 0: the one-token kernels (scratch: floats [top * ff]); mode 1: the grouped prompt-row kernels (scratch: ints moe work
+// table, then floats [tokens * top * (2 * ff + width)])
+void nt_b200_moe_glu_experts(float* y, const float* h, const int* sel, const float* wt, const void* const* gate_tab, const void* const* up_tab,
+                             const void* const* down_tab, int dtype, int experts, int top, int ff, int width, int tokens, int mode, void* scratch, void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MoeWeights w;
+    w.gate = gate_tab; w.up = up_tab; w.down = down_tab; w.dtype = (nt::DType)dtype; w.experts = experts; w.top = top; w.ff = ff; w.width = width;
+    if (mode == 0) {
+        float* act = static_cast<float*>(scratch);
+        moe_expert_up_token(act, h, sel, w, s);
+        moe_expert_down_token(y, act, sel, wt, nullptr, nullptr, w, s);
+        return;
+    }
+    int* work = static_cast<int*>(scratch);
+    const size_t wi = (moe_work_ints(tokens, experts, top) + 3) & ~(size_t)3;
+    float* act_rows = reinterpret_cast<float*>(work + wi);
+    float* gate_rows = act_rows + (size_t)tokens * top * ff;
+    float* y_rows = gate_rows + (size_t)tokens * top * ff;
+    moe_group(work, sel, tokens, experts, top, s);
+    moe_expert_gate_rows(gate_rows, h, work, w, tokens, s);
+    moe_expert_up_rows(act_rows, h, work, w, tokens, s);
+    glu_bias_mul(act_rows, gate_rows, act_rows, nullptr, nullptr, tokens * top, ff, false, s);
+    moe_expert_down_rows(y_rows, act_rows, work, w, tokens, s);
+    moe_combine(y, y_rows, work, wt, nullptr, nullptr, tokens, experts, top, width, s);
 }
 void nt_b200_glu_mul(float* out, const float* gate, const float* up, long long n, int gelu, void* stream) {
     glu_mul(out, gate, up, (size_t)n, gelu != 0, static_cast<cudaStream_t>(stream));

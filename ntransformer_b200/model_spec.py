@@ -210,3 +210,109 @@ def vebotar_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype=
                 t[p + "mlp.shared.down"] = mat(W, mlp["shared"]["ff"])
                 t[p + "mlp.shared.sg"] = mat(1, W, torch.float32)
     return t
+
+
+# ---- Tanolorn (layer-spec family, model folders): synthetic configurations and random device weights for benchmarks ----
+def tanolorn_config(vocab=32000, width=4096, pattern=("mamba2", "latent_attention", "mamba2", "latent_attention"), kv_from=None, mlp=("dense", "moe", "moe", "moe"),
+                    heads=32, dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, rot_base=10000.0,
+                    s_heads=64, s_vdim=64, state=128, groups=8, conv=4, norm_groups=8, ff=8192, experts=16, top=4, eff=1408, route_groups=(4, 2), side=256,
+                    eps=1e-6):
+    """The family's config.json as a dict.  pattern: mixer type per layer; mlp: feed-forward kind per layer ("dense", "moe" or None);
+    kv_from: {layer: earlier latent-attention layer whose cache rows it reads}; route_groups: (count, keep) or None; side: width of the
+    per-layer token input (0: none)."""
+    kv_from = kv_from or {}
+    layers = []
+    for i, typ in enumerate(pattern):
+        if typ == "latent_attention":
+            m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5,
+                 "rot": {"dims": rot_dim, "base": rot_base}}
+            if i in kv_from:
+                m["kv_from"] = kv_from[i]
+        else:
+            m = {"heads": s_heads, "vdim": s_vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}
+        k = mlp[i % len(mlp)]
+        if k == "dense":
+            f = {"kind": "dense", "ff": ff}
+        elif k == "moe":
+            r = {"experts": experts, "top": top}
+            if route_groups:
+                r["groups"] = {"count": route_groups[0], "keep": route_groups[1]}
+            f = {"kind": "moe", "expert": {"ff": eff}, "router": r}
+        else:
+            f = None
+        layers.append({"type": typ, "mixer": m, "mlp": f})
+    cfg = {"architecture": "Tanolorn", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if side:
+        cfg["token_side"] = {"dim": side}
+    return cfg
+
+
+def tanolorn_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype=None):
+    """Checkpoint name -> random CUDA tensor (matrices `dtype`, default bfloat16; gains, biases, convolution taps, scan constants, router
+    rows and the choice correction float32)."""
+    import math
+
+    import torch
+
+    dtype = dtype or torch.bfloat16
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W, side = config["width"], (config.get("token_side") or {}).get("dim", 0)
+    n_layers = len(config["layers"])
+
+    def mat(rows, cols, dt=dtype):
+        return (torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32) * cols ** -0.5).to(dt)
+
+    def vec(n, mean=0.0, std=0.1):
+        return mean + std * torch.randn(n, generator=g, device=device, dtype=torch.float32)
+
+    def uni(n, lo, hi):
+        return lo + (hi - lo) * torch.rand(n, generator=g, device=device, dtype=torch.float32)
+
+    t = {"embed": mat(config["vocab"], W) * W ** 0.5, "final.norm": vec(W), "head": mat(config["vocab"], W)}
+    if side:
+        t["side.embed"] = mat(config["vocab"], n_layers * side) * (n_layers * side) ** 0.5
+    for i, e in enumerate(config["layers"]):
+        m, p = e["mixer"], "l%d." % i
+        t[p + "norm1"] = vec(W)
+        if e["type"] == "latent_attention":
+            t[p + "mix.dq"] = mat(m["q_rank"], W)
+            t[p + "mix.dq.norm"] = vec(m["q_rank"], 1.0)
+            t[p + "mix.uq"] = mat(m["heads"] * (m["dim"] + m["rot_dim"]), m["q_rank"])
+            if "kv_from" not in m:
+                t[p + "mix.dkv"] = mat(m["kv_rank"] + m["rot_dim"], W)
+                t[p + "mix.dkv.norm"] = vec(m["kv_rank"], 1.0)
+            t[p + "mix.uk"] = mat(m["heads"] * m["dim"], m["kv_rank"])
+            t[p + "mix.uv"] = mat(m["heads"] * m["vdim"], m["kv_rank"])
+            t[p + "mix.o"] = mat(W, m["heads"] * m["vdim"])
+        else:
+            inner = m["heads"] * m["vdim"]
+            ch = inner + 2 * m["groups"] * m["state"]
+            t[p + "mix.in"] = mat(inner + ch + m["heads"], W)
+            t[p + "mix.conv"] = mat(ch, m["conv"], torch.float32)
+            t[p + "mix.conv.b"] = vec(ch)
+            t[p + "mix.dt_bias"] = uni(m["heads"], -4.0, -1.0)
+            t[p + "mix.A_log"] = torch.log(uni(m["heads"], 1.0, 8.0))
+            t[p + "mix.D"] = vec(m["heads"], 1.0)
+            t[p + "mix.norm"] = vec(inner, 1.0)
+            t[p + "mix.o"] = mat(W, inner)
+        f = e.get("mlp")
+        if f:
+            t[p + "norm2"] = vec(W)
+            if f["kind"] == "dense":
+                for n, (r, c) in (("gate", (f["ff"], W)), ("up", (f["ff"], W)), ("down", (W, f["ff"]))):
+                    t[p + "mlp." + n] = mat(r, c)
+                    t[p + "mlp." + n + ".b"] = vec(r)
+            else:
+                E, eff = f["router"]["experts"], f["expert"]["ff"]
+                t[p + "mlp.router"] = mat(E, W, torch.float32)
+                t[p + "mlp.correction"] = vec(E, 0.0, 0.05)
+                for x in range(E):
+                    t[p + "mlp.e%d.gate" % x] = mat(eff, W)
+                    t[p + "mlp.e%d.up" % x] = mat(eff, W)
+                    t[p + "mlp.e%d.down" % x] = mat(W, eff)
+        if side:
+            t[p + "side.gate"] = mat(side, W)
+            t[p + "side.proj"] = mat(W, side)
+            t[p + "side.norm"] = vec(W, 1.0)
+    return t

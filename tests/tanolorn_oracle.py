@@ -52,12 +52,18 @@ def rotate_half(v, pos, dims, base):
     return out
 
 
+def rotate_for(v, pos, m):
+    """The mixer's rotation, or none when its configuration has no \"rot\"."""
+    r = m.get("rot")
+    return rotate_half(v, pos, r["dims"], r["base"]) if r and r["dims"] else v
+
+
 def latent_kv(X, P, p, m, eps, pos):
     """What a latent-attention layer caches: the normed latent [T, kv_rank] and the shared rotated key part [T, rot_dim]."""
     r = m["kv_rank"]
     d = X @ P[p + "mix.dkv"].T
     c = norm_plain(d[:, :r], P[p + "mix.dkv.norm"], eps)
-    kr = rotate_half(d[:, r:], pos, m["rot"]["dims"], m["rot"]["base"])
+    kr = rotate_for(d[:, r:], pos, m)
     return c, kr
 
 
@@ -69,7 +75,7 @@ def latent_attention(X, P, p, m, eps, pos, kv):
     cq = norm_plain(X @ P[p + "mix.dq"].T, P[p + "mix.dq.norm"], eps)
     q = (cq @ P[p + "mix.uq"].T).reshape(T, H, D + R)
     qn = q[:, :, :D]
-    qr = rotate_half(q[:, :, D:], pos, m["rot"]["dims"], m["rot"]["base"])
+    qr = rotate_for(q[:, :, D:], pos, m)
     kn = (c @ P[p + "mix.uk"].T).reshape(-1, H, D)
     v = (c @ P[p + "mix.uv"].T).reshape(-1, H, V)
     out = np.zeros((T, H, V))
@@ -196,3 +202,96 @@ def forward(cfg, P, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(X.copy())
     return norm_zero_centred(X, P["final.norm"], eps) @ P["head"].T
+
+
+# ---------------------------------------------------------------- random models for the tests
+def _bf16(a):
+    """Round to values bfloat16 holds exactly, so that a 16-bit checkpoint and the float64 oracle see the same weights."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    u = a.view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+def random_model(rng, vocab=41, width=40, pattern=("scan", "latent", "scan", "latent"), kv_from=None, mlp=("dense", "moe", "moe", None),
+                 heads=3, dim=8, rot_dim=6, vdim=10, q_rank=12, kv_rank=20, rot_dims=None, base=50.0, scale=None,
+                 s_heads=4, s_vdim=6, state=12, groups=2, conv=4, norm_groups=2,
+                 ff=24, experts=6, top=2, eff=10, route_groups=(3, 2), side=5, eps=1e-5, corr_shift=0.0):
+    """(config dict, weights dict).  pattern: mixer per layer; mlp: feed-forward kind per layer (None: none); kv_from: {layer: earlier
+    latent layer whose cache rows it reads}; route_groups: (count, keep) or None; side: width of the per-layer token input (0: none)."""
+    kv_from = kv_from or {}
+    layers = []
+    for i, kind in enumerate(pattern):
+        if kind == "latent":
+            m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+                 "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5)}
+            if rot_dim:
+                m["rot"] = {"dims": rot_dim if rot_dims is None else rot_dims, "base": base}
+            if i in kv_from:
+                m["kv_from"] = kv_from[i]
+            typ = "latent_attention"
+        else:
+            m = {"heads": s_heads, "vdim": s_vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}
+            typ = "mamba2"
+        k = mlp[i % len(mlp)]
+        if k == "dense":
+            f = {"kind": "dense", "ff": ff}
+        elif k == "moe":
+            r = {"experts": experts, "top": top}
+            if route_groups:
+                r["groups"] = {"count": route_groups[0], "keep": route_groups[1]}
+            f = {"kind": "moe", "expert": {"ff": eff}, "router": r}
+        else:
+            f = None
+        layers.append({"type": typ, "mixer": m, "mlp": f})
+    cfg = {"architecture": "Tanolorn", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if side:
+        cfg["token_side"] = {"dim": side}
+    mat = lambda r, c, s=1.0: _bf16(rng.standard_normal((r, c)) * s * c ** -0.5)
+    gain0 = lambda n: _bf16(0.2 * rng.standard_normal(n))          # stored around zero
+    gain1 = lambda n: _bf16(1.0 + 0.2 * rng.standard_normal(n))
+    W = {"embed": _bf16(rng.standard_normal((vocab, width))), "final.norm": gain0(width), "head": mat(vocab, width)}
+    if side:
+        W["side.embed"] = _bf16(rng.standard_normal((vocab, len(layers) * side)))
+    for i, e in enumerate(layers):
+        p, m = "l%d." % i, e["mixer"]
+        W[p + "norm1"] = gain0(width)
+        if e["type"] == "latent_attention":
+            W[p + "mix.dq"] = mat(q_rank, width)
+            W[p + "mix.dq.norm"] = gain1(q_rank)
+            W[p + "mix.uq"] = mat(heads * (dim + rot_dim), q_rank, 1.5)
+            if "kv_from" not in m:
+                W[p + "mix.dkv"] = mat(kv_rank + rot_dim, width)
+                W[p + "mix.dkv.norm"] = gain1(kv_rank)
+            W[p + "mix.uk"] = mat(heads * dim, kv_rank, 1.5)
+            W[p + "mix.uv"] = mat(heads * vdim, kv_rank)
+            W[p + "mix.o"] = mat(width, heads * vdim)
+        else:
+            inner, ch = s_heads * s_vdim, s_heads * s_vdim + 2 * groups * state
+            W[p + "mix.in"] = mat(inner + ch + s_heads, width)
+            W[p + "mix.conv"] = _bf16(rng.standard_normal((ch, conv)) * conv ** -0.5)
+            W[p + "mix.conv.b"] = _bf16(0.1 * rng.standard_normal(ch))
+            W[p + "mix.dt_bias"] = _bf16(rng.uniform(-3.0, 0.5, s_heads))
+            W[p + "mix.A_log"] = _bf16(np.log(rng.uniform(0.5, 4.0, s_heads)))
+            W[p + "mix.D"] = _bf16(1.0 + 0.3 * rng.standard_normal(s_heads))
+            W[p + "mix.norm"] = gain1(inner)
+            W[p + "mix.o"] = mat(width, inner)
+        f = e["mlp"]
+        if f:
+            W[p + "norm2"] = gain0(width)
+            if f["kind"] == "dense":
+                for n, (r, c) in (("gate", (ff, width)), ("up", (ff, width)), ("down", (width, ff))):
+                    W[p + "mlp." + n] = mat(r, c)
+                    W[p + "mlp." + n + ".b"] = _bf16(0.2 * rng.standard_normal(r))
+            else:
+                W[p + "mlp.router"] = mat(experts, width, 2.0)
+                W[p + "mlp.correction"] = _bf16(0.3 * rng.standard_normal(experts) + corr_shift)
+                for x in range(experts):
+                    W[p + "mlp.e%d.gate" % x] = mat(eff, width)
+                    W[p + "mlp.e%d.up" % x] = mat(eff, width)
+                    W[p + "mlp.e%d.down" % x] = mat(width, eff)
+        if side:
+            W[p + "side.gate"] = mat(side, width)
+            W[p + "side.proj"] = mat(width, side)
+            W[p + "side.norm"] = gain1(width)
+    return cfg, W

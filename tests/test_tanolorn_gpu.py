@@ -1,0 +1,482 @@
+"""Tanolorn on the GPU against the plain float64 oracle (tests/tanolorn_oracle.py): each mechanism's kernel alone, then whole models
+through the engine's step function — prompt pass vs token-by-token decoding, portions down to two tokens, cache rows and scan state
+reused by a second request, keys far away, the first tokens, odd sizes, long decoding with and without graph replay, and greedy
+generation through the engine's own entry point."""
+import numpy as np
+import pytest
+import torch
+
+import tanolorn_oracle as O
+from tanolorn_util import device_tensors
+from zelunex_util import rel_rms, write_model_dir
+
+from ntransformer_b200._lib import lib
+from ntransformer_b200.dtypes import DType
+from ntransformer_b200.engine import Engine, Model
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dt=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda().to(dt).contiguous()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def host(t):
+    return t.double().cpu().numpy()
+
+
+# ---------------------------------------------------------------- kernels alone
+@pytest.mark.parametrize("cache", [DType.F32, DType.BF16])
+@pytest.mark.parametrize("q_rank,kv_rank,rot_dim,dims,inter", [(12, 20, 6, 6, 0), (300, 70, 10, 4, 0), (8, 16, 8, 8, 1), (5, 9, 0, 0, 0)])
+def test_latent_rows_norms_rotation_and_cache_write(cache, q_rank, kv_rank, rot_dim, dims, inter):
+    rng = np.random.default_rng(q_rank)
+    T, p0, n, eps, base = 7, 29, 48, 1e-5, 37.0
+    cq = rng.standard_normal((T, q_rank)); dkv = rng.standard_normal((T, kv_rank + rot_dim)) * 3
+    gq = 1 + 0.2 * rng.standard_normal(q_rank); gk = 1 + 0.2 * rng.standard_normal(kv_rank)
+    tdt = torch.float32 if cache == DType.F32 else torch.bfloat16
+    CQ, DKV, GQ, GK = dev(cq), dev(dkv), dev(gq), dev(gk)
+    kc = torch.zeros(n, kv_rank + rot_dim, device="cuda", dtype=tdt)
+    lib().nt_b200_latent_prep(CQ.data_ptr(), q_rank, GQ.data_ptr(), DKV.data_ptr(), kv_rank, rot_dim, GK.data_ptr(), eps, kc.data_ptr(), int(cache), dims, inter,
+                              base, T, p0, stream())
+    pos = np.arange(p0, p0 + T)
+    np.testing.assert_allclose(host(CQ), O.norm_plain(cq, host(GQ), eps), rtol=2e-5, atol=2e-5)
+    c = O.norm_plain(dkv[:, :kv_rank], host(GK), eps)
+    kr = dkv[:, kv_rank:]
+    if dims and not inter:
+        kr = O.rotate_half(kr, pos, dims, base)
+    elif dims:                                      # pairs (2i, 2i+1): the same rotation in another channel order
+        perm = np.concatenate([np.arange(0, dims, 2), np.arange(1, dims, 2), np.arange(dims, rot_dim)])
+        kr = O.rotate_half(kr[:, perm], pos, dims, base)[:, np.argsort(perm)]
+    tol = 3e-5 if cache == DType.F32 else 1.5e-2
+    np.testing.assert_allclose(host(kc[p0:p0 + T]), np.concatenate([c, kr], axis=1), rtol=tol, atol=tol)
+    assert float(kc[:p0].abs().max()) == 0 and float(kc[p0 + T:].abs().max()) == 0
+    # a layer that reads another layer's rows: the query latent is normed, the cache is left alone
+    CQ2 = dev(cq); before = kc.clone()
+    lib().nt_b200_latent_prep(CQ2.data_ptr(), q_rank, GQ.data_ptr(), None, kv_rank, rot_dim, None, eps, kc.data_ptr(), int(cache), dims, inter, base, T, p0, stream())
+    assert torch.equal(CQ2, CQ) and torch.equal(before, kc)
+
+
+def latent_reference(q, rows, W_uk, W_uv, pos, H, D, R, V, kv_rank, dims, base, scale):
+    """One query row q [H * (D + R)] at position pos over cache rows [n, kv_rank + R] -> [H * V], keys and values expanded per head."""
+    c, kr = rows[:pos + 1, :kv_rank], rows[:pos + 1, kv_rank:]
+    out = np.zeros((H, V))
+    for h in range(H):
+        qh = q[h * (D + R):(h + 1) * (D + R)]
+        qr = O.rotate_half(qh[None, D:], [pos], dims, base)[0] if dims else qh[D:]
+        kn = c @ W_uk[h * D:(h + 1) * D].T
+        s = (kn @ qh[:D] + kr @ qr) * scale
+        w = np.exp(s - s.max()); w /= w.sum()
+        out[h] = w @ (c @ W_uv[h * V:(h + 1) * V].T)
+    return out.reshape(-1)
+
+
+def run_latent(q, rows_dev, cache, W_uk, W_uv, wdt, T, p0, H, D, R, V, kv_rank, dims, base, scale, n):
+    Q = dev(q)
+    qa = torch.zeros(T, H * (kv_rank + R), device="cuda"); ol = torch.zeros(T, H * kv_rank, device="cuda"); out = torch.zeros(T, H * V, device="cuda")
+    lib().nt_b200_latent_q_absorb(qa.data_ptr(), Q.data_ptr(), W_uk.data_ptr(), int(wdt), T, H, D, R, kv_rank, dims, 0, base, p0, stream())
+    lib().nt_b200_attention_rows(ol.data_ptr(), qa.data_ptr(), rows_dev.data_ptr(), int(cache), T, p0, H, kv_rank + R, kv_rank, kv_rank + R, scale, n, stream())
+    lib().nt_b200_latent_v_up(out.data_ptr(), ol.data_ptr(), W_uv.data_ptr(), int(wdt), T, H, V, kv_rank, stream())
+    return host(out)
+
+
+@pytest.mark.parametrize("cache", [DType.F32, DType.BF16])
+@pytest.mark.parametrize("H,D,R,V,kv_rank,dims", [(3, 8, 6, 10, 20, 6), (1, 16, 8, 8, 64, 8), (5, 4, 2, 3, 7, 2), (2, 24, 16, 40, 300, 12), (2, 6, 0, 5, 9, 0)])
+def test_latent_attention_in_the_latent_space(cache, H, D, R, V, kv_rank, dims):
+    """Scores and the weighted sum are taken on the cached rows themselves (the key up-projection moves to the query side, the value
+    up-projection behind the sum): same answers as expanding every head's keys and values, for prompts, portions and decoded tokens."""
+    rng = np.random.default_rng(H * 10 + D)
+    n, base, scale = 90, 50.0, (D + R) ** -0.5
+    tdt = torch.float32 if cache == DType.F32 else torch.bfloat16
+    rows_dev = dev(rng.standard_normal((n, kv_rank + R)), tdt)
+    W_uk = dev(rng.standard_normal((H * D, kv_rank)) * kv_rank ** -0.5, tdt); W_uv = dev(rng.standard_normal((H * V, kv_rank)) * kv_rank ** -0.5, tdt)
+    rows, uk, uv = host(rows_dev), host(W_uk), host(W_uv)
+    for p0, T in ((0, n), (37, 20), (n - 1, 1), (0, 1), (5, 2)):
+        q = rng.standard_normal((T, H * (D + R)))
+        got = run_latent(q, rows_dev, cache, W_uk, W_uv, cache, T, p0, H, D, R, V, kv_rank, dims, base, scale, n)
+        ref = np.stack([latent_reference(q[t], rows, uk, uv, p0 + t, H, D, R, V, kv_rank, dims, base, scale) for t in range(T)])
+        np.testing.assert_allclose(got, ref, rtol=5e-5, atol=5e-5)
+
+
+@pytest.mark.parametrize("T", [1, 24])
+@pytest.mark.parametrize("far", [0, 1, 255, 256, 257, 700, 998, 999])
+def test_one_loud_key_among_a_thousand(T, far):
+    """Row `far` is made to match the last query exactly: the output must be that row's value, wherever the row lies — the first
+    rows, the borders of the key slices a decoded token's cluster of CTAs takes, the row before the query and the query's own."""
+    rng = np.random.default_rng(far)
+    H, D, R, V, kv_rank, n = 2, 8, 4, 6, 16, 1000
+    rows = rng.standard_normal((n, kv_rank + R)) * 0.1
+    uk = np.zeros((H * D, kv_rank)); uv = rng.standard_normal((H * V, kv_rank))
+    for h in range(H):
+        uk[h * D:(h + 1) * D, :D] = np.eye(D)                   # the unrotated key of a row is its first D latent numbers
+    rows[far, :D] = 3.0
+    q = rng.standard_normal((T, H * (D + R))) * 0.1
+    q[-1] = 0.0
+    for h in range(H):
+        q[-1, h * (D + R):h * (D + R) + D] = 4.0                # 8 * 12 against scores of order 0.1 elsewhere
+    rows_dev, W_uk, W_uv = dev(rows), dev(uk), dev(uv)
+    got = run_latent(q, rows_dev, DType.F32, W_uk, W_uv, DType.F32, T, n - T, H, D, R, V, kv_rank, 0, 10.0, 1.0, n)
+    want = (rows[far, :kv_rank] @ uv.T)
+    np.testing.assert_allclose(got[-1], want, rtol=1e-4, atol=1e-4)
+    ref = latent_reference(q[-1], rows, uk, uv, n - 1, H, D, R, V, kv_rank, 0, 10.0, 1.0)
+    np.testing.assert_allclose(got[-1], ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("taps,ch", [(4, 37), (1, 5), (2, 300), (7, 12)])
+def test_causal_convolution_carries_its_last_inputs(taps, ch):
+    rng = np.random.default_rng(taps)
+    T, ld, col0 = 40, ch + 9, 4
+    u = rng.standard_normal((T, ld)); w = rng.standard_normal((ch, taps)); b = rng.standard_normal(ch)
+    ref = O.silu(O.causal_conv(u[:, col0:col0 + ch], w, b))
+    Wd, Bd = dev(w), dev(b)
+    for sizes in ([T], [1] * T, [2, 1, 3, 30, 2, 2], [5, 35], [1, 1, 38]):       # portions shorter than the taps too
+        state = torch.full((max(1, taps - 1), ch), 7.0, device="cuda")             # stale numbers of an earlier sequence
+        got, pos = [], 0
+        for n in sizes:
+            U = dev(u[pos:pos + n]); out = torch.zeros(n, ch, device="cuda")
+            lib().nt_b200_ssm_conv(out.data_ptr(), U.data_ptr(), ld, col0, state.data_ptr(), Wd.data_ptr(), Bd.data_ptr(), n, ch, taps, pos, stream())
+            got.append(host(out)); pos += n
+        np.testing.assert_allclose(np.concatenate(got), ref, rtol=2e-5, atol=2e-5)
+
+
+def scan_reference(xbc, dt_raw, dt_bias, A_log, D, H, V, N, G):
+    T = xbc.shape[0]
+    inner = H * V
+    x = xbc[:, :inner].reshape(T, H, V); B = xbc[:, inner:inner + G * N].reshape(T, G, N); Cm = xbc[:, inner + G * N:].reshape(T, G, N)
+    dt = O.softplus(dt_raw + dt_bias)
+    S = np.zeros((H, N, V)); y = np.zeros((T, H, V))
+    for t in range(T):
+        for h in range(H):
+            g = h // (H // G)
+            S[h] = np.exp(-np.exp(A_log[h]) * dt[t, h]) * S[h] + dt[t, h] * np.outer(B[t, g], x[t, h])
+            y[t, h] = S[h].T @ Cm[t, g] + D[h] * x[t, h]
+    return y.reshape(T, inner)
+
+
+@pytest.mark.parametrize("H,V,N,G", [(4, 6, 12, 2), (1, 1, 1, 1), (6, 3, 40, 3), (2, 5, 130, 1), (3, 33, 32, 3), (2, 4, 256, 2)])
+def test_scan_recurrence_and_state_hand_over(H, V, N, G):
+    rng = np.random.default_rng(N)
+    T = 50
+    inner, ch = H * V, H * V + 2 * G * N
+    xbc = rng.standard_normal((T, ch)); dt_raw = rng.standard_normal((T, H)) * 2
+    dt_bias = rng.uniform(-3, 1, H); A_log = np.log(rng.uniform(0.3, 4, H)); D = rng.standard_normal(H)
+    ref = scan_reference(xbc, dt_raw, dt_bias, A_log, D, H, V, N, G)
+    ld = 3 + H
+    u = np.zeros((T, ld)); u[:, 3:] = dt_raw
+    Bi, Al, Dd = dev(dt_bias), dev(A_log), dev(D)
+    for sizes in ([T], [1] * T, [2, 3, 40, 2, 2, 1], [30, 20]):
+        state = torch.full((H, V, N), 3.0, device="cuda")                       # must be ignored at position 0
+        got, pos = [], 0
+        for n in sizes:
+            X = dev(xbc[pos:pos + n]); U = dev(u[pos:pos + n]); y = torch.zeros(n, inner, device="cuda")
+            lib().nt_b200_ssm_scan(y.data_ptr(), X.data_ptr(), U.data_ptr(), ld, 3, state.data_ptr(), Bi.data_ptr(), Al.data_ptr(), Dd.data_ptr(), n, H, V, N, G,
+                                   pos, stream())
+            got.append(host(y)); pos += n
+        np.testing.assert_allclose(np.concatenate(got), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_scan_large_steps_and_slow_decay():
+    """Step sizes far beyond 20 (no clamp: softplus(z) = z there) and a decay so slow that the first token still counts after 400."""
+    rng = np.random.default_rng(3)
+    H, V, N, G, T = 2, 3, 8, 1, 400
+    inner, ch = H * V, H * V + 2 * G * N
+    xbc = rng.standard_normal((T, ch)); dt_raw = rng.standard_normal((T, H)); dt_raw[7] = 45.0
+    xbc[0, :inner] = 50.0                                                          # a loud first token
+    dt_bias = np.array([-4.0, 0.0]); A_log = np.log(np.array([1e-3, 1.0])); D = np.zeros(H)
+    ref = scan_reference(xbc, dt_raw, dt_bias, A_log, D, H, V, N, G)
+    quiet = xbc.copy(); quiet[0, :inner] = 0.0
+    assert np.abs(ref[-1, :V] - scan_reference(quiet, dt_raw, dt_bias, A_log, D, H, V, N, G)[-1, :V]).max() > 1e-2     # head 0 still remembers it
+    state = torch.zeros(H, V, N, device="cuda")
+    u = np.zeros((T, H)); u[:] = dt_raw
+    Bi, Al, Dd = dev(dt_bias), dev(A_log), dev(D)
+    got, pos = [], 0
+    for n in [390] + [1] * 10:
+        X = dev(xbc[pos:pos + n]); U = dev(u[pos:pos + n]); y = torch.zeros(n, inner, device="cuda")
+        lib().nt_b200_ssm_scan(y.data_ptr(), X.data_ptr(), U.data_ptr(), H, 0, state.data_ptr(), Bi.data_ptr(), Al.data_ptr(), Dd.data_ptr(),
+                               n, H, V, N, G, pos, stream())
+        got.append(host(y)); pos += n
+    got = np.concatenate(got)
+    np.testing.assert_allclose(got, ref, rtol=2e-4, atol=2e-4 * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("inner,groups", [(24, 2), (24, 1), (30, 5), (512, 4), (7, 7)])
+def test_gate_then_grouped_norm(inner, groups):
+    rng = np.random.default_rng(inner)
+    T, ld, z0, eps = 5, inner + 6, 2, 1e-5
+    y = rng.standard_normal((T, inner)) * 4; u = rng.standard_normal((T, ld)); gain = 1 + 0.3 * rng.standard_normal(inner)
+    out = torch.zeros(T, inner, device="cuda")
+    Y, U, G = dev(y), dev(u), dev(gain)                    # named: a temporary's memory may be handed out again before the kernel runs
+    lib().nt_b200_ssm_gate_norm(out.data_ptr(), Y.data_ptr(), U.data_ptr(), ld, z0, G.data_ptr(), eps, T, inner, groups, stream())
+    v = y * O.silu(u[:, z0:z0 + inner])
+    ref = O.rms(v.reshape(T, groups, inner // groups), eps).reshape(T, inner) * gain
+    np.testing.assert_allclose(host(out), ref, rtol=3e-5, atol=3e-5)
+
+
+def test_post_norm_add_biased_gate_and_token_side_rows():
+    rng = np.random.default_rng(5)
+    T, W, eps = 6, 45, 1e-5
+    x = rng.standard_normal((T, W)); y = rng.standard_normal((T, W)) * 5; g = 1 + 0.2 * rng.standard_normal(W); b = rng.standard_normal(W)
+    Y, G, Bv = dev(y), dev(g), dev(b)
+    for bias in (None, b):
+        X = dev(x)
+        lib().nt_b200_add_rmsnorm_rows(X.data_ptr(), Y.data_ptr(), G.data_ptr(), Bv.data_ptr() if bias is not None else None, T, W, eps, stream())
+        np.testing.assert_allclose(host(X), x + O.norm_plain(y + (bias if bias is not None else 0), g, eps), rtol=3e-5, atol=3e-5)
+    F = 13
+    ga = rng.standard_normal((T, F)) * 3; up = rng.standard_normal((T, F)); bg = rng.standard_normal(F); bu = rng.standard_normal(F)
+    out = torch.zeros(T, F, device="cuda")
+    GA, UP, BG, BU = dev(ga), dev(up), dev(bg), dev(bu)
+    lib().nt_b200_glu_bias_mul(out.data_ptr(), GA.data_ptr(), UP.data_ptr(), BG.data_ptr(), BU.data_ptr(), T, F, 0, stream())
+    np.testing.assert_allclose(host(out), O.silu(ga + bg) * (up + bu), rtol=3e-5, atol=3e-5)
+    lib().nt_b200_glu_bias_mul(out.data_ptr(), GA.data_ptr(), UP.data_ptr(), None, None, T, F, 1, stream())
+    np.testing.assert_allclose(host(out), O.gelu_tanh(ga) * up, rtol=3e-5, atol=3e-5)
+    vocab, layers, dim = 11, 3, 4
+    E = dev(rng.standard_normal((vocab, layers * dim)), torch.bfloat16)
+    toks = rng.integers(0, vocab, T).astype(np.int32)
+    TK = torch.from_numpy(toks).cuda()
+    for layer in range(layers):
+        sg = rng.standard_normal((T, dim)) * 2
+        G = dev(sg)
+        lib().nt_b200_side_gate_rows(G.data_ptr(), E.data_ptr(), int(DType.BF16), layers * dim, layer * dim, TK.data_ptr(), T, dim, stream())
+        np.testing.assert_allclose(host(G), O.gelu_tanh(sg) * host(E)[toks][:, layer * dim:(layer + 1) * dim], rtol=3e-5, atol=3e-5)
+
+
+@pytest.mark.parametrize("experts,top,groups,keep,shift", [(6, 2, 3, 2, 0.0), (16, 3, 2, 1, 0.0), (8, 2, 0, 0, 0.0), (8, 4, 4, 2, -3.0), (6, 2, 6, 3, -2.0),
+                                                          (70, 5, 7, 3, 0.0), (4, 4, 1, 1, 0.0)])
+def test_router_scores_correction_and_groups(experts, top, groups, keep, shift):
+    """The choice looks at sigmoid(logit) + correction inside the best groups only; the weights are the plain scores.  With a
+    correction that makes every choice score negative, a group that is out must not come back as a zero."""
+    rng = np.random.default_rng(experts * 7 + top)
+    T, W = 40, 24
+    h = rng.standard_normal((T, W)); router = rng.standard_normal((experts, W)) * 0.4; corr = 0.3 * rng.standard_normal(experts) + shift
+    P = {"mlp.router": router, "mlp.correction": corr}
+    mlp = {"router": {"experts": experts, "top": top}}
+    if groups:
+        mlp["router"]["groups"] = {"count": groups, "keep": keep}
+    rsel, rwt = O.route(h, P, "", mlp)
+    sel = torch.zeros(T, top, device="cuda", dtype=torch.int32); wt = torch.zeros(T, top, device="cuda")
+    Hd, Rd, Cd = dev(h), dev(router), dev(corr)
+    lib().nt_b200_moe_route_scored(sel.data_ptr(), wt.data_ptr(), Hd.data_ptr(), Rd.data_ptr(), Cd.data_ptr(), experts, top, groups, keep, W, T, stream())
+    assert np.array_equal(sel.cpu().numpy(), rsel)
+    np.testing.assert_allclose(host(wt), rwt, rtol=2e-5, atol=2e-5)
+    if shift < 0:
+        assert (1 / (1 + np.exp(-(h @ router.T))) + corr).max() < 0
+    lib().nt_b200_moe_route_scored(sel.data_ptr(), wt.data_ptr(), Hd.data_ptr(), Rd.data_ptr(), None, experts, top, groups, keep, W, T, stream())
+    P["mlp.correction"] = np.zeros(experts)
+    assert np.array_equal(sel.cpu().numpy(), O.route(h, P, "", mlp)[0])
+
+
+@pytest.mark.parametrize("dt", [DType.F32, DType.BF16])
+@pytest.mark.parametrize("experts,top,ff,W", [(5, 2, 10, 24), (3, 3, 7, 9), (9, 1, 64, 128)])
+def test_gated_experts_token_and_grouped_forms(dt, experts, top, ff, W):
+    rng = np.random.default_rng(ff)
+    T = 33
+    tdt = torch.float32 if dt == DType.F32 else torch.bfloat16
+    mats = {k: [dev(rng.standard_normal(shape) * shape[1] ** -0.5, tdt) for _ in range(experts)] for k, shape in (("gate", (ff, W)), ("up", (ff, W)), ("down", (W, ff)))}
+    tabs = {k: torch.tensor([m.data_ptr() for m in v], dtype=torch.int64, device="cuda") for k, v in mats.items()}
+    h = rng.standard_normal((T, W))
+    sel = np.stack([rng.permutation(experts)[:top] for _ in range(T)]).astype(np.int32); wt = rng.uniform(0.1, 1, (T, top))
+    ref = np.zeros((T, W))
+    for t in range(T):
+        for k in range(top):
+            e = sel[t, k]
+            a = O.silu(h[t] @ host(mats["gate"][e]).T) * (h[t] @ host(mats["up"][e]).T)
+            ref[t] += wt[t, k] * (a @ host(mats["down"][e]).T)
+    H, SEL, WT = dev(h), torch.from_numpy(sel).cuda(), dev(wt)
+    y = torch.zeros(T, W, device="cuda")
+    scratch = torch.zeros(4 * (experts + 2 * T * top + experts + 8) + 4 * T * top * (2 * ff + W) + 64, device="cuda", dtype=torch.uint8)
+    lib().nt_b200_moe_glu_experts(y.data_ptr(), H.data_ptr(), SEL.data_ptr(), WT.data_ptr(), tabs["gate"].data_ptr(), tabs["up"].data_ptr(), tabs["down"].data_ptr(),
+                                  int(dt), experts, top, ff, W, T, 1, scratch.data_ptr(), stream())
+    np.testing.assert_allclose(host(y), ref, rtol=1e-4, atol=1e-4)
+    for t in (0, T - 1):
+        y1 = torch.zeros(W, device="cuda")
+        lib().nt_b200_moe_glu_experts(y1.data_ptr(), H[t].data_ptr(), SEL[t].data_ptr(), WT[t].data_ptr(), tabs["gate"].data_ptr(), tabs["up"].data_ptr(),
+                                      tabs["down"].data_ptr(), int(dt), experts, top, ff, W, 1, 0, scratch.data_ptr(), stream())
+        np.testing.assert_allclose(host(y1), ref[t], rtol=1e-4, atol=1e-4)
+
+
+# ---------------------------------------------------------------- whole models through the engine
+def build(cfg, W, exact, max_context=256):
+    return Model.from_config_json(cfg, device_tensors(W, exact), max_context=max_context, exact_f32=exact)
+
+
+def run_portions(model, toks, sizes):
+    rows, pos = [], 0
+    for n in sizes:
+        rows.append(model.forward_logits(toks[pos:pos + n], pos, list(range(n))))
+        pos += n
+    assert pos == len(toks)
+    return np.concatenate(rows)
+
+
+def per_position(a, b):
+    a = np.asarray(a, dtype=np.float64); b = np.asarray(b, dtype=np.float64)
+    a = a - a.mean(-1, keepdims=True); b = b - b.mean(-1, keepdims=True)
+    return np.sqrt(((a - b) ** 2).mean(-1)) / np.sqrt((b ** 2).mean())
+
+
+CONFIGS = {
+    "base": dict(kv_from={3: 1}),
+    "attention_only_shared_rows": dict(pattern=("latent", "latent", "latent"), kv_from={1: 0, 2: 0}, mlp=("moe", None, "dense")),
+    "scan_only_no_side": dict(pattern=("scan", "scan"), mlp=("moe", "dense"), side=0, route_groups=None, groups=1, norm_groups=1, conv=2),
+    "one_of_everything": dict(pattern=("latent", "scan"), heads=1, s_heads=1, s_vdim=1, state=1, groups=1, norm_groups=1, conv=1, experts=1, top=1, route_groups=(1, 1),
+                              mlp=("moe", "moe"), side=1, dim=2, rot_dim=2, vdim=1, q_rank=1, kv_rank=2, width=6, vocab=9, ff=3, eff=2),
+    "partial_rotation_negative_choice": dict(pattern=("scan", "latent"), rot_dim=10, rot_dims=4, mlp=("moe", "moe"), corr_shift=-2.5, experts=8, top=3,
+                                             route_groups=(4, 2), state=40, s_heads=6, groups=3, s_vdim=5, norm_groups=3, conv=5),
+    "no_rotation_wide_latent": dict(pattern=("latent", "scan", "latent"), kv_from={2: 0}, rot_dim=0, kv_rank=300, q_rank=70, mlp=("dense", "dense", "moe"),
+                                    route_groups=(6, 6), state=130, side=9),
+    # tile-aligned matrices: with BF16 weights the projections run on the tensor cores
+    "tensor_core_tiles": dict(pattern=("scan", "latent"), width=128, q_rank=64, kv_rank=128, heads=2, dim=32, rot_dim=32, vdim=64, s_heads=4, s_vdim=32, state=16,
+                              groups=1, ff=128, eff=128, experts=4, top=2, route_groups=(2, 1), mlp=("dense", "moe"), side=64, vocab=128),
+}
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("exact", [True, False])
+def test_model_schedules_agree_with_oracle(name, exact):
+    rng = np.random.default_rng(len(name))
+    cfg, W = O.random_model(rng, **CONFIGS[name])
+    S = 61
+    toks = rng.integers(0, cfg["vocab"], S).astype(np.int32)
+    ref = O.forward(cfg, W, toks)
+    m = build(cfg, W, exact)
+
+    def close(got):
+        if exact:
+            return rel_rms(got, ref) < 3e-4
+        # 16-bit cache rows, and a choice score within rounding of the next one may pick the other expert at a position
+        err = per_position(got, ref)
+        return np.median(err) < 1.5e-2 and err.max() < 0.25
+
+    whole = run_portions(m, toks, [S])
+    assert close(whole)
+    single = run_portions(m, toks, [1] * S)
+    assert close(single)
+    mixed = run_portions(m, toks, [2, 17, 3, 2, 20, 5, 1, 1, 8, 2])      # portions cut anywhere, shorter than the convolution too
+    assert close(mixed)
+    assert close(run_portions(m, toks, [40] + [1] * 21))
+    if exact:                                                            # how a prompt is cut changes rounding only
+        assert rel_rms(single, whole) < 1e-4 and rel_rms(mixed, whole) < 1e-4
+    m.close()
+
+
+def test_residual_after_every_mechanism_matches():
+    """Layer by layer: models of one layer each, so that a fault names its mechanism."""
+    for k, kw in enumerate((dict(pattern=("latent",), mlp=(None,), side=0), dict(pattern=("scan",), mlp=(None,), side=0),
+                            dict(pattern=("scan",), mlp=("dense",), side=0), dict(pattern=("scan",), mlp=("moe",), side=0),
+                            dict(pattern=("scan",), mlp=(None,), side=7))):
+        rng = np.random.default_rng(k)
+        cfg, W = O.random_model(rng, **kw)
+        toks = rng.integers(0, cfg["vocab"], 30).astype(np.int32)
+        m = build(cfg, W, True)
+        assert rel_rms(run_portions(m, toks, [30]), O.forward(cfg, W, toks)) < 1e-4, kw
+        m.close()
+
+
+def test_first_tokens_and_single_token_request():
+    rng = np.random.default_rng(2)
+    cfg, W = O.random_model(rng, kv_from={3: 1})
+    toks = rng.integers(0, cfg["vocab"], 5).astype(np.int32)
+    ref = O.forward(cfg, W, toks)
+    m = build(cfg, W, True)
+    assert rel_rms(run_portions(m, toks[:1], [1]), ref[:1]) < 2e-4
+    assert rel_rms(run_portions(m, toks, [2, 3]), ref) < 2e-4
+    assert rel_rms(run_portions(m, toks, [1, 1, 1, 2]), ref) < 2e-4
+
+
+def test_rows_and_state_are_reused_between_requests():
+    """A second request starts at position 0 over the first one's cache rows, convolution inputs and scan state: bit-equal to running alone."""
+    rng = np.random.default_rng(21)
+    cfg, W = O.random_model(rng, kv_from={3: 1})
+    a = rng.integers(0, cfg["vocab"], 50).astype(np.int32)
+    b = rng.integers(0, cfg["vocab"], 30).astype(np.int32)
+    for first in ([50], [20] + [1] * 30):
+        m = build(cfg, W, True)
+        run_portions(m, a, first)
+        after_a = run_portions(m, b, [18] + [1] * 12)
+        m2 = build(cfg, W, True)
+        alone = run_portions(m2, b, [18] + [1] * 12)
+        np.testing.assert_array_equal(after_a, alone)
+        assert rel_rms(alone, O.forward(cfg, W, b)) < 2e-4
+        after_a = run_portions(m, b[:3], [1, 1, 1])                      # and again, decoding from the very first token
+        np.testing.assert_array_equal(after_a, run_portions(m2, b[:3], [1, 1, 1]))
+
+
+def test_long_decode_and_graph_replay():
+    rng = np.random.default_rng(8)
+    cfg, W = O.random_model(rng, pattern=("scan", "latent"), mlp=("moe", "dense"), width=32, vocab=50)
+    S = 300
+    toks = rng.integers(0, cfg["vocab"], S).astype(np.int32)
+    ref = O.forward(cfg, W, toks)
+    m = build(cfg, W, True, max_context=512)
+    assert rel_rms(run_portions(m, toks, [3] + [1] * (S - 3)), ref) < 3e-4
+    m.use_graph(False)
+    m.clear_kv()
+    assert rel_rms(run_portions(m, toks, [3] + [1] * (S - 3)), ref) < 3e-4
+
+
+def loud_first_key(W, D=8, R=6, heads=3):
+    """Token 0 writes a loud latent channel 0 and every other token's query looks for exactly that channel: among hundreds of
+    ordinary keys the one row of token 0 takes nearly all the weight, wherever it lies."""
+    W["embed"][:, :2] = 0.0; W["embed"][0, 0] = 6.0; W["embed"][1:, 1] = 2.0
+    W["l0.mix.dkv"][0, :] = 0.0; W["l0.mix.dkv"][0, 0] = 4.0
+    W["l0.mix.dq"][0, :] = 0.0; W["l0.mix.dq"][0, 1] = 3.0
+    for h in range(heads):
+        W["l0.mix.uk"][h * D, :] = 0.0; W["l0.mix.uk"][h * D, 0] = 2.0
+        W["l0.mix.uq"][h * (D + R), :] = 0.0; W["l0.mix.uq"][h * (D + R), 0] = 2.0
+
+
+@pytest.mark.parametrize("pattern", [("latent",), ("scan",)])
+def test_a_far_token_reaches_the_last_position(pattern):
+    """One layer, so the mixer is the only path between positions.  A token that occurs nowhere else sits far back (rows 0 and 2 of
+    600): the last logits must follow the oracle in a prompt, across portions and when decoding, and the oracle itself must move."""
+    rng = np.random.default_rng(13)
+    cfg, W = O.random_model(rng, pattern=pattern, mlp=(None,), side=0, scale=1.0)
+    if pattern == ("scan",):
+        W["l0.mix.A_log"] = O._bf16(np.log(np.full(4, 2e-3)))            # a slow decay keeps the far token alive
+    else:
+        loud_first_key(W)
+    S = 600
+    toks = rng.integers(1, cfg["vocab"], S).astype(np.int32)
+    base = O.forward(cfg, W, toks)
+    m = build(cfg, W, True, max_context=1024)
+    for special_at in (0, 2):
+        t = toks.copy(); t[special_at] = 0
+        ref = O.forward(cfg, W, t)
+        assert rel_rms(ref[-1:], base[-1:]) > 1e-3
+        for sizes in ([S], [256, 300] + [1] * 44, [3, 597]):
+            got = run_portions(m, t, sizes)
+            assert rel_rms(got[-40:], ref[-40:]) < 3e-4
+    m.close()
+
+
+def test_greedy_generation_through_the_engine(tmp_path):
+    rng = np.random.default_rng(4)
+    cfg, W = O.random_model(rng, kv_from={3: 1})
+    d = write_model_dir(tmp_path / "m", cfg, W)
+    prompt = rng.integers(0, cfg["vocab"], 19).astype(np.int32)
+    for exact in (True, False):
+        e = Engine()
+        assert e.load_path(d, max_context=128, exact_f32=exact)
+        assert e.vocab_size == cfg["vocab"] and e.n_layers == 4
+        new = e.generate_ids(prompt, max_tokens=24, temperature=0.0)
+        assert len(new) == 24
+        assert e.generate_ids(prompt, max_tokens=24, temperature=0.0) == new       # rows and state are taken over from position 0
+        logits = O.forward(cfg, W, np.concatenate([prompt, np.asarray(new, dtype=np.int32)]))
+        for i, tok in enumerate(new):                                         # every generated id is the oracle's greedy choice
+            row = logits[len(prompt) - 1 + i]
+            assert row[tok] >= row.max() - (1e-3 if exact else 0.1), (exact, i)
+        sampled = e.generate_ids(prompt, max_tokens=8, temperature=0.8, top_k=10, top_p=0.9, repeat_penalty=1.1, seed=7)
+        assert len(sampled) == 8 and all(0 <= s < cfg["vocab"] for s in sampled)
+        e.close()
+
+
+def test_model_folder_loads_like_device_tensors(tmp_path):
+    rng = np.random.default_rng(6)
+    cfg, W = O.random_model(rng, kv_from={3: 1})
+    toks = rng.integers(0, cfg["vocab"], 33).astype(np.int32)
+    a = Model.load_dir(write_model_dir(tmp_path / "m", cfg, W), max_context=64, exact_f32=True)
+    b = build(cfg, W, True, max_context=64)
+    np.testing.assert_array_equal(a.forward_logits(toks, 0, [0, 5, 32]), b.forward_logits(toks, 0, [0, 5, 32]))
