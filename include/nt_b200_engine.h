@@ -82,6 +82,9 @@ void nt_b200_latent_prep(float* cq, int q_rank, const float* q_gain, const float
 void nt_b200_latent_q_absorb(float* qa, const float* q, const void* W_uk, int dtype, int tokens, int heads, int dim, int rot_dim, int kv_rank, int rot_dims,
                              int interleaved, float rot_base, int p0, void* stream);
 void nt_b200_latent_v_up(float* out, const float* ol, const void* W_uv, int dtype, int tokens, int heads, int vdim, int kv_rank, void* stream);
+/* prompt portions (16 tokens or more, BF16 cache rows): per-head keys / values expanded once, then tiled tensor-core attention; -1: widths not covered */
+int nt_b200_latent_attention_expanded(float* out, const float* q, const void* cache, const void* W_uk, const void* W_uv, int dtype, int tokens, int p0, int heads,
+                                      int dim, int rot_dim, int vdim, int kv_rank, int rot_dims, int interleaved, float rot_base, float scale, void* stream);
 /* full causal attention over ONE key / value head stored as rows of `row` numbers: keys the first dim, values the first vdim of a row */
 void nt_b200_attention_rows(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,
                             int max_seq, void* stream);

@@ -9,6 +9,10 @@
 //                    rest, both written to cache row pos (skipped for a layer that reads another layer's rows)
 //   latent_q_absorb  qa = [W_uk,h^T q_unrotated | rot(q_rotated)] for every head, tiles of 8 tokens per CTA
 //   latent_v_up      out = W_uv,h o_latent per head, tiles of 8 tokens per CTA
+// A prompt portion of 16 tokens or more instead expands the rows it can see into per-head keys and values once (two tensor-core GEMMs
+// over the latents: latent_rows_f32 feeds them, latent_expand_pack packs their results with the rotated key part into 16-bit
+// [row, head, width] operands) and runs the tiled tensor-core attention kernel over them (attention_heads_mma): heads * (dim + rot_dim +
+// vdim) multiply-adds per (query, key) instead of heads * (2 kv_rank + rot_dim).  latent_q_rot_pad rotates and pads the queries.
 // Rotation: channel i of the rotated part pairs with channel i + dims/2 (or 2i with 2i+1), angle pos * base^(-2i/dims), computed
 // in double and applied in F32; channels past `dims` pass unchanged.  Norms, angles and sums are F32 or better.
 // Compiled WITHOUT --use_fast_math.
@@ -156,6 +160,62 @@ __global__ void __launch_bounds__(256) latent_v_up_kernel(float* __restrict__ ou
     }
 }
 
+// ---- per-head keys and values of a prompt portion (the tiled attention kernel reads 16-bit [row, head, width] operands) ----
+
+// out [n, kv_rank] F32 <- the latents of cache rows r0 .. r0 + n - 1
+__global__ void __launch_bounds__(256) latent_rows_f32_kernel(float* __restrict__ out, const __nv_bfloat16* __restrict__ cache, int row, int kv_rank, int r0, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (e >= total) return;
+    const size_t r = e / kv_rank;
+    const int i = (int)(e % kv_rank);
+    out[e] = wld(cache, ((size_t)r0 + r) * row + i);
+}
+
+// kfull [r, h, kw] = [ku[r - r0, h, :dim] | rotated key part of row r | 0 ...]; vfull [r, h, vw] = [vu[r - r0, h, :vdim] | 0 ...]
+__global__ void __launch_bounds__(256) latent_expand_pack_kernel(__nv_bfloat16* __restrict__ kfull, __nv_bfloat16* __restrict__ vfull, const float* __restrict__ ku,
+                                                                 const float* __restrict__ vu, const __nv_bfloat16* __restrict__ cache, int row, int kv_rank,
+                                                                 int r0, int heads, int dim, int rot_dim, int vdim, int kw, int vw) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, h = blockIdx.y;
+    const size_t ar = (size_t)r0 + r;
+    for (int i = threadIdx.x; i < kw; i += 256) {
+        __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+        if (i < dim) v = __float2bfloat16_rn(ku[((size_t)r * heads + h) * dim + i]);
+        else if (i < dim + rot_dim) v = cache[ar * row + kv_rank + (i - dim)];
+        kfull[(ar * heads + h) * kw + i] = v;
+    }
+    for (int i = threadIdx.x; i < vw; i += 256)
+        vfull[(ar * heads + h) * vw + i] = __float2bfloat16_rn(i < vdim ? vu[((size_t)r * heads + h) * vdim + i] : 0.f);
+}
+
+// qp [t, h, kw] = [q[t, h, :dim] | rot(q[t, h, dim:]) | 0 ...]
+__global__ void __launch_bounds__(256) latent_q_rot_pad_kernel(float* __restrict__ qp, const float* __restrict__ q, int heads, int dim, int rot_dim, int kw, int dims,
+                                                               int interleaved, double log2_base, int p0) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y, qd = dim + rot_dim;
+    const float* src = q + ((size_t)t * heads + h) * qd;
+    float* dst = qp + ((size_t)t * heads + h) * kw;
+    for (int i = threadIdx.x; i < kw; i += 256) {
+        float v = 0.f;
+        if (i < dim) v = src[i];
+        else if (i < qd) v = rotated(src + dim, i - dim, dims, interleaved, log2_base, p0 + t);
+        dst[i] = v;
+    }
+}
+
+// out [t, h * vdim + i] = o [t, h, vw][i]
+__global__ void __launch_bounds__(256) latent_unpad_kernel(float* __restrict__ out, const float* __restrict__ o, int vdim, int vw, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (e >= total) return;
+    out[e] = o[e / vdim * vw + e % vdim];
+}
+
 }  // namespace
 
 void latent_prep(float* cq, int q_rank, const float* q_gain, const float* dkv, int kv_rank, int rot_dim, const float* kv_gain, float eps, void* cache,
@@ -196,6 +256,38 @@ void latent_v_up(float* out, const float* ol, const void* W_uv, DType dt, int T,
     if (dt == DType::F32) NT_VU(float); else if (dt == DType::F16) NT_VU(__half); else if (dt == DType::BF16) NT_VU(__nv_bfloat16);
     else NT_CHECK(false, "latent_v_up: dense dtypes only");
 #undef NT_VU
+    count_launch();
+}
+
+void latent_rows_f32(float* out, const void* cache, DType cache_dt, int row, int kv_rank, int r0, int n, cudaStream_t s) {
+    if (n <= 0) return;
+    NT_CHECK(cache_dt == DType::BF16, "latent_rows_f32: BF16 cache rows");
+    const size_t total = (size_t)n * kv_rank;
+    launch_k(latent_rows_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, out, static_cast<const __nv_bfloat16*>(cache), row, kv_rank, r0, total);
+    count_launch();
+}
+
+void latent_expand_pack(void* kfull, void* vfull, const float* ku, const float* vu, const void* cache, DType cache_dt, int kv_rank, int r0, int n, int heads,
+                        int dim, int rot_dim, int vdim, int kw, int vw, cudaStream_t s) {
+    if (n <= 0) return;
+    NT_CHECK(cache_dt == DType::BF16, "latent_expand_pack: BF16 cache rows");
+    NT_CHECK(kw >= dim + rot_dim && vw >= vdim, "latent_expand_pack: padded widths below the head's");
+    launch_k(latent_expand_pack_kernel, dim3(n, heads), dim3(256), 0, s, static_cast<__nv_bfloat16*>(kfull), static_cast<__nv_bfloat16*>(vfull), ku, vu,
+             static_cast<const __nv_bfloat16*>(cache), kv_rank + rot_dim, kv_rank, r0, heads, dim, rot_dim, vdim, kw, vw);
+    count_launch();
+}
+
+void latent_q_rot_pad(float* qp, const float* q, int T, int heads, int dim, int rot_dim, int kw, int rot_dims, bool interleaved, float rot_base, int p0,
+                      cudaStream_t s) {
+    if (T <= 0) return;
+    launch_k(latent_q_rot_pad_kernel, dim3(T, heads), dim3(256), 0, s, qp, q, heads, dim, rot_dim, kw, rot_dims, interleaved ? 1 : 0, std::log2((double)rot_base), p0);
+    count_launch();
+}
+
+void latent_unpad(float* out, const float* o, int T, int heads, int vdim, int vw, cudaStream_t s) {
+    const size_t total = (size_t)T * heads * vdim;
+    if (!total) return;
+    launch_k(latent_unpad_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, out, o, vdim, vw, total);
     count_launch();
 }
 

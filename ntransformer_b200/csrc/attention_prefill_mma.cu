@@ -252,4 +252,27 @@ void attention_window_mma(float* out, const float* Q, const void* kc, const void
 #undef NT_AW
 }
 
+// Per-head 16-bit operands built for the call (latent attention's expanded keys / values): key width 64, 128 or 192, value width 64
+// or 128, every head its own key / value head, full causal mask.
+bool attention_heads_mma_widths(int key_dim, int value_dim, int* kw, int* vw) {
+    if (key_dim <= 0 || value_dim <= 0 || key_dim > 192 || value_dim > 128) return false;
+    *kw = key_dim <= 64 ? 64 : key_dim <= 128 ? 128 : 192;
+    *vw = value_dim <= 64 ? 64 : 128;
+    return true;
+}
+void attention_heads_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int rows, int heads, int kw, int vw, float scale,
+                         cudaStream_t s) {
+    const __half* k = static_cast<const __half*>(kc);
+    const __half* v = static_cast<const __half*>(vc);
+#define NT_AH(D, V) launch<D, V, true>(out, Q, k, v, tokens, p0, heads, heads, rows, scale, 0, 0, 0.f, s)
+    if (kw == 64 && vw == 64) NT_AH(64, 64);
+    else if (kw == 64 && vw == 128) NT_AH(64, 128);
+    else if (kw == 128 && vw == 64) NT_AH(128, 64);
+    else if (kw == 128 && vw == 128) NT_AH(128, 128);
+    else if (kw == 192 && vw == 64) NT_AH(192, 64);
+    else if (kw == 192 && vw == 128) NT_AH(192, 128);
+    else NT_CHECK(false, "attention_heads_mma: widths from attention_heads_mma_widths");
+#undef NT_AH
+}
+
 }}  // namespace nt::b200

@@ -237,6 +237,31 @@ void nt_b200_latent_q_absorb(float* qa, const float* q, const void* W_uk, int dt
 void nt_b200_latent_v_up(float* out, const float* ol, const void* W_uv, int dtype, int tokens, int heads, int vdim, int kv_rank, void* stream) {
     latent_v_up(out, ol, W_uv, (nt::DType)dtype, tokens, heads, vdim, kv_rank, static_cast<cudaStream_t>(stream));
 }
+// The prompt-portion form of latent attention: every visible row's per-head keys and values expanded once (F32 GEMMs here, the engine
+// uses its tensor-core GEMM where the matrices qualify), packed as 16-bit operands, then the tiled tensor-core attention kernel.
+// cache: BF16 rows [rows, kv_rank + rot_dim] with rows >= p0 + tokens.  Scratch is allocated and freed here.  -1: head widths not covered.
+int nt_b200_latent_attention_expanded(float* out, const float* q, const void* cache, const void* W_uk, const void* W_uv, int dtype, int tokens, int p0, int heads,
+                                      int dim, int rot_dim, int vdim, int kv_rank, int rot_dims, int interleaved, float rot_base, float scale, void* stream) {
+    int kw = 0, vw = 0;
+    if (tokens < 16 || !attention_heads_mma_widths(dim + rot_dim, vdim, &kw, &vw)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t P = (size_t)p0 + tokens, H = (size_t)heads;
+    float *c32 = nullptr, *ku = nullptr, *vu = nullptr, *qp = nullptr, *op = nullptr;
+    void *kf = nullptr, *vf = nullptr;
+    NT_CUDA_CHECK(cudaMalloc(&c32, sizeof(float) * P * kv_rank)); NT_CUDA_CHECK(cudaMalloc(&ku, sizeof(float) * P * H * dim)); NT_CUDA_CHECK(cudaMalloc(&vu, sizeof(float) * P * H * vdim));
+    NT_CUDA_CHECK(cudaMalloc(&qp, sizeof(float) * tokens * H * kw)); NT_CUDA_CHECK(cudaMalloc(&op, sizeof(float) * tokens * H * vw));
+    NT_CUDA_CHECK(cudaMalloc(&kf, 2 * P * H * kw)); NT_CUDA_CHECK(cudaMalloc(&vf, 2 * P * H * vw));
+    latent_rows_f32(c32, cache, nt::DType::BF16, kv_rank + rot_dim, kv_rank, 0, (int)P, s);
+    gemm_dense(ku, c32, W_uk, (nt::DType)dtype, 0, (int)P, heads * dim, kv_rank, DENSE_STORE, nullptr, 1.f, s);
+    gemm_dense(vu, c32, W_uv, (nt::DType)dtype, 0, (int)P, heads * vdim, kv_rank, DENSE_STORE, nullptr, 1.f, s);
+    latent_expand_pack(kf, vf, ku, vu, cache, nt::DType::BF16, kv_rank, 0, (int)P, heads, dim, rot_dim, vdim, kw, vw, s);
+    latent_q_rot_pad(qp, q, tokens, heads, dim, rot_dim, kw, rot_dims, interleaved != 0, rot_base, p0, s);
+    attention_heads_mma(op, qp, kf, vf, tokens, p0, (int)P, heads, kw, vw, scale, s);
+    latent_unpad(out, op, tokens, heads, vdim, vw, s);
+    NT_CUDA_CHECK(cudaStreamSynchronize(s));
+    for (void* p : {(void*)c32, (void*)ku, (void*)vu, (void*)qp, (void*)op, kf, vf}) cudaFree(p);
+    return 0;
+}
 // Full causal attention of `heads` query heads over ONE key / value head whose rows live in `cache` with `row` numbers per position:
 // keys are the first `dim` numbers of a row, values its first `vdim` (the latent-attention layout: dim = row, vdim = kv_rank).
 void nt_b200_attention_rows(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,

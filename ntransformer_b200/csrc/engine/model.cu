@@ -77,7 +77,8 @@ Model::~Model() {
     for (size_t i = 0; i < kcs_.size(); i++) if (kcs_[i] && (cache_owned_.empty() || cache_owned_[i])) { cudaFree(kcs_[i]); cudaFree(vcs_[i]); }
     for (void* p : {(void*)pf_.h, (void*)pf_.tmp, pf_.hws, (void*)want_out_, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt,
                     (void*)pf_.sgate, (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)streams_, (void*)sub_y_, (void*)maps_out_, (void*)moe_sel_,
-                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_, (void*)pf_.g2, pf_.moe_ws, (void*)pf_.gate_rows})
+                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_, (void*)pf_.g2, pf_.moe_ws, pf_.moe_ws2, (void*)pf_.gate_rows, lat_.k, lat_.v, lat_.ws, (void*)lat_.q, (void*)lat_.o, (void*)lat_.c32,
+                    (void*)lat_.ku, (void*)lat_.vu})
         if (p) cudaFree(p);
     if (moe_offsets_host_) cudaFreeHost(moe_offsets_host_);
     for (LayerWeights& L : layers_)

@@ -173,6 +173,18 @@ private:
     int* moe_offsets_host_ = nullptr;     // pinned: per-expert row offsets of the current prompt chunk (tensor-core expert GEMMs)
     float* ident_tab_ = nullptr;          // {1}: mixing matrix and write gain of a single residual stream
     Weight side_embd_;                    // second token embedding [vocab, layers * side_dim] (ModelConfig::side_dim)
+    // Latent attention over a prompt portion: every visible position's per-head keys [P, heads, kd] and values [P, heads, vd] (16-bit,
+    // widths padded to what the tiled attention kernel takes), rebuilt from the latent rows for each layer and portion; the portion's
+    // rotated, padded queries and padded outputs; F32 staging of one block of rows for the two up-projections.
+    struct LatentScratch {
+        size_t rows = 0, tokens = 0, kw = 0, vw = 0, stage_w = 0, rank = 0;
+        void *k = nullptr, *v = nullptr, *ws = nullptr;
+        float *q = nullptr, *o = nullptr, *c32 = nullptr, *ku = nullptr, *vu = nullptr;
+    } lat_;
+    bool latent_expand_ok(const LayerSpec& S, int T) const;
+    void ensure_latent_scratch(const LayerSpec& S, size_t rows, size_t tokens);
+    void latent_attention_rows(int i, int T, int p0, const float* q, float* out, cudaStream_t s);   // out [T, heads * vdim]
+    bool moe_glu_rows_tc(int i, int T, const float* x, cudaStream_t s);    // routed gated experts of a prompt portion on the tensor cores -> pf_.y_rows
     RowBufs dec_;                         // POST_NORM decode step: x is hidden_, the rest one scratch row each (stable addresses for the graph)
     std::vector<int> want_;               // places (indices into the current forward's tokens) whose logits are collected
     float* want_out_ = nullptr;           // device [want_cap_, vocab]
@@ -235,6 +247,7 @@ private:
         float *xs = nullptr, *maps = nullptr;     // STREAMS: the residual streams [T, S, width]; attention maps' outputs [T, heads * maps * vdim]
         int *sel = nullptr, *work = nullptr;      // mixture of experts: chosen experts [T, top]; grouping tables
         float *g2 = nullptr; void *moe_ws = nullptr;   // tensor-core experts: rows gathered in expert order [T*top, width]; per-expert padded split workspace
+        void *moe_ws2 = nullptr;                       // gated tensor-core experts: the split of act(gate) * up, input of the down GEMMs
         float *gate_rows = nullptr;                    // gated experts: W_gate h of the grouped rows [T*top, ff]
         float *wt = nullptr, *sgate = nullptr, *act_rows = nullptr, *y_rows = nullptr;   // weights [T, top], shared gate [T], grouped rows [T*top, ff | width]
     } pf_;

@@ -400,8 +400,9 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream_));
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, (void*)pf_.g, (void*)pf_.u, (void*)pf_.h, (void*)pf_.tmp,
                     pf_.ws, pf_.ws2, pf_.hws, (void*)pf_.tok, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt, (void*)pf_.sgate,
-                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws, (void*)pf_.gate_rows})
+                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws, pf_.moe_ws2, (void*)pf_.gate_rows})
         if (p) cudaFree(p);
+    pf_.moe_ws2 = nullptr;
     pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = pf_.g2 = pf_.gate_rows = nullptr; pf_.sel = pf_.work = nullptr; pf_.moe_ws = nullptr;
     const size_t T = (size_t)((tokens + 127) / 128 * 128), hidden = (size_t)cfg_.hidden_size;
     size_t qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1, mapmax = 1, topmax = 0, emax = 1, effmax = 1;
@@ -438,6 +439,7 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     pf_.tok = dmalloc<int>(T);
     pf_.ws = pf_.ws2 = pf_.hws = nullptr;
     if (post_form && topmax > 0) pf_.gate_rows = dmalloc<float>(T * topmax * effmax);      // the gate half of the gated experts' rows
+    if (post_form && topmax > 0 && !exact32_) pf_.moe_ws2 = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)(T * topmax + emax * 128), (int)effmax));
     bool any_tc = false;
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerWeights& L = layer_weights(i);
@@ -456,10 +458,10 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     pf_.cap = (int)T;
 }
 
-// BF16 rows that the tcgen05 GEMM can read in place through TMA (rows % 128, cols % 64, 16-byte aligned); never in exact mode.
+// BF16 rows that the tcgen05 GEMM can read in place through TMA (rows >= 128 and % 4, cols % 64, 16-byte aligned); never in exact mode.
 bool Model::spec_tc_ok(const Weight& w) const {
     static const bool off = getenv("NT_B200_NO_TC_PREFILL") != nullptr;
-    return !exact32_ && !off && w.dtype == DType::BF16 && gemm_f16_tc_supported(w.ptr, w.rows, w.cols, w.pitch);
+    return !exact32_ && !off && w.dtype == DType::BF16 && gemm_f16_tc_ragged_supported(w.ptr, w.rows, w.cols, w.pitch);
 }
 
 // C (ep)= A . W^T for T prompt rows: on the tensor cores from the BF16 hi/lo split of A when the matrix qualifies, else in FP32
@@ -519,7 +521,7 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
             spec_gemm(pf_.x, pf_.attn, o_tc ? pf_.ws : nullptr, L.wo, T, DENSE_SCALED_ADD, L.ls1, m, s);
             if (S.ff > 0) {
                 const bool gelu = S.act == GluAct::GELU_TANH, down_tc = spec_tc_ok(L.down);
-                if (spec_tc_ok(L.gate) && spec_tc_ok(L.up) && down_tc) {
+                if (spec_tc_ok(L.gate) && spec_tc_ok(L.up) && down_tc && S.ff % 128 == 0) {
                     // gate / up GEMMs with the gated activation and the split for the down projection in the epilogue: the
                     // [T, ff] activations never reach HBM in FP32
                     TcOpts o; o.bf16 = true; o.gelu = gelu;
@@ -711,6 +713,87 @@ void Model::rows_matmul(float* C, const float* A, const Weight& w, int T, cudaSt
     spec_gemm(C, A, tc ? pf_.ws : nullptr, w, T, DENSE_STORE, nullptr, 1.f, s);
 }
 
+// ---- latent attention over a prompt portion: expanded per-head keys / values and the tiled tensor-core attention kernel ----
+
+constexpr int LATENT_ROW_BLOCK = 2048;      // cache rows expanded per pair of up-projection GEMMs
+
+// 16 queries or more, BF16 cache rows, head widths the tiled kernel takes; never in exact mode (the absorbed form is all F32 there).
+bool Model::latent_expand_ok(const LayerSpec& S, int T) const {
+    static const bool off = getenv("NT_B200_NO_LATENT_EXPAND") != nullptr;
+    int kw = 0, vw = 0;
+    return !off && !exact32_ && cache_dt_ == DType::BF16 && T >= 16 && attention_heads_mma_widths(S.dim + S.latent.rot_dim, S.vdim, &kw, &vw);
+}
+
+void Model::ensure_latent_scratch(const LayerSpec& S, size_t rows, size_t tokens) {
+    int kw = 0, vw = 0;
+    NT_CHECK(attention_heads_mma_widths(S.dim + S.latent.rot_dim, S.vdim, &kw, &vw), "latent attention: head widths outside the tiled kernel's");
+    const size_t H = (size_t)S.heads, need_k = H * kw, need_v = H * vw, need_stage = H * (size_t)std::max(S.dim, S.vdim), need_rank = (size_t)S.latent.kv_rank;
+    if (rows <= lat_.rows && tokens <= lat_.tokens && need_k <= lat_.kw && need_v <= lat_.vw && need_stage <= lat_.stage_w && need_rank <= lat_.rank) return;
+    NT_CUDA_CHECK(cudaStreamSynchronize(stream_));
+    for (void* p : {lat_.k, lat_.v, lat_.ws, (void*)lat_.q, (void*)lat_.o, (void*)lat_.c32, (void*)lat_.ku, (void*)lat_.vu}) if (p) cudaFree(p);
+    if (rows > lat_.rows) lat_.rows = std::min((size_t)cfg_.max_seq_len, std::max(2 * lat_.rows, (rows + 1023) / 1024 * 1024));     // grows geometrically up to the cache's length
+    lat_.rows = std::max(lat_.rows, rows);
+    lat_.tokens = std::max(lat_.tokens, (tokens + 127) / 128 * 128);
+    lat_.kw = std::max(lat_.kw, need_k); lat_.vw = std::max(lat_.vw, need_v); lat_.stage_w = std::max(lat_.stage_w, need_stage); lat_.rank = std::max(lat_.rank, need_rank);
+    lat_.k = dmalloc<uint16_t>(lat_.rows * lat_.kw); lat_.v = dmalloc<uint16_t>(lat_.rows * lat_.vw);
+    lat_.q = dmalloc<float>(lat_.tokens * lat_.kw); lat_.o = dmalloc<float>(lat_.tokens * lat_.vw);
+    lat_.c32 = dmalloc<float>((size_t)LATENT_ROW_BLOCK * lat_.rank);
+    lat_.ws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes(LATENT_ROW_BLOCK, (int)lat_.rank));
+    lat_.ku = dmalloc<float>((size_t)LATENT_ROW_BLOCK * lat_.stage_w); lat_.vu = dmalloc<float>((size_t)LATENT_ROW_BLOCK * lat_.stage_w);
+}
+
+// q [T, heads, dim + rot_dim] (unrotated) at positions p0..; the layer's cache rows 0 .. p0 + T - 1 are written.  out [T, heads * vdim].
+void Model::latent_attention_rows(int i, int T, int p0, const float* q, float* out, cudaStream_t s) {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    const LayerWeights& L = layer_weights(i);
+    const LatentSpec& A = S.latent;
+    int kw = 0, vw = 0;
+    attention_heads_mma_widths(S.dim + A.rot_dim, S.vdim, &kw, &vw);
+    const int P = p0 + T, row = A.kv_rank + A.rot_dim;
+    ensure_latent_scratch(S, (size_t)P, (size_t)T);
+    const bool tk = spec_tc_ok(L.w_uk), tv = spec_tc_ok(L.w_uv);
+    for (int r0 = 0; r0 < P; r0 += LATENT_ROW_BLOCK) {
+        const int n = std::min(LATENT_ROW_BLOCK, P - r0);
+        latent_rows_f32(lat_.c32, kcs_[(size_t)i], cache_dt_, row, A.kv_rank, r0, n, s);
+        if (tk || tv) split_activations(lat_.ws, lat_.c32, n, A.kv_rank, s, true);
+        spec_gemm(lat_.ku, lat_.c32, tk ? lat_.ws : nullptr, L.w_uk, n, DENSE_STORE, nullptr, 1.f, s);
+        spec_gemm(lat_.vu, lat_.c32, tv ? lat_.ws : nullptr, L.w_uv, n, DENSE_STORE, nullptr, 1.f, s);
+        latent_expand_pack(lat_.k, lat_.v, lat_.ku, lat_.vu, kcs_[(size_t)i], cache_dt_, A.kv_rank, r0, n, S.heads, S.dim, A.rot_dim, S.vdim, kw, vw, s);
+    }
+    latent_q_rot_pad(lat_.q, q, T, S.heads, S.dim, A.rot_dim, kw, S.rot.dims, S.rot.interleaved, S.rot.base, p0, s);
+    float* o = vw == S.vdim ? out : lat_.o;
+    attention_heads_mma(o, lat_.q, lat_.k, lat_.v, T, p0, P, S.heads, kw, vw, S.scale, s);
+    if (o != out) latent_unpad(out, lat_.o, T, S.heads, S.vdim, vw, s);
+}
+
+// The routed gated experts of T prompt rows on the tensor cores: the per-expert row counts come to the host (one small copy and a wait),
+// then every expert with rows runs, over exactly its rows, the gate / up GEMM pair whose epilogue applies silu(gate) * up and writes the
+// down GEMM's split input, and the down GEMM.  pf_.y_rows [T * top, width] in the grouped order.  false: some matrix does not qualify.
+bool Model::moe_glu_rows_tc(int i, int T, const float* x, cudaStream_t s) {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    const LayerWeights& L = layer_weights(i);
+    const int hidden = cfg_.hidden_size;
+    if (!pf_.moe_ws || !pf_.moe_ws2 || !pf_.g2 || !moe_offsets_host_ || S.ff % 128 != 0 || S.experts > 256) return false;
+    for (int e = 0; e < S.experts; e++)
+        if (!spec_tc_ok(L.e_gate[(size_t)e]) || !spec_tc_ok(L.e_up[(size_t)e]) || !spec_tc_ok(L.e_down[(size_t)e])) return false;
+    NT_CUDA_CHECK(cudaMemcpyAsync(moe_offsets_host_, pf_.work, sizeof(int) * (size_t)(S.experts + 1), cudaMemcpyDeviceToHost, s));
+    NT_CUDA_CHECK(cudaStreamSynchronize(s));
+    moe_gather_rows(pf_.g2, x, pf_.work, T, S.experts, S.top, hidden, s);
+    TcOpts o; o.bf16 = true;
+    size_t padded = 0;
+    for (int e = 0; e < S.experts; e++) {
+        const int r0 = moe_offsets_host_[e], cnt = moe_offsets_host_[e + 1] - r0;
+        if (cnt <= 0) continue;
+        void* wi = static_cast<uint8_t*>(pf_.moe_ws) + gemm_f16_tc_workspace_bytes((int)padded, hidden);
+        void* wo = static_cast<uint8_t*>(pf_.moe_ws2) + gemm_f16_tc_workspace_bytes((int)padded, S.ff);
+        split_activations(wi, pf_.g2 + (size_t)r0 * hidden, cnt, hidden, s, true);
+        NT_CHECK(gemm_f16_tc_swiglu_ws(wo, wi, L.e_gate[(size_t)e].ptr, L.e_up[(size_t)e].ptr, cnt, S.ff, hidden, s, o), "expert GEMM (gate / up) rejected");
+        NT_CHECK(gemm_f16_tc_ws(pf_.y_rows + (size_t)r0 * hidden, wo, L.e_down[(size_t)e].ptr, cnt, hidden, S.ff, false, s, o), "expert GEMM (down) rejected");
+        padded += ((size_t)cnt + 127) / 128 * 128;
+    }
+    return true;
+}
+
 // One layer over T rows: x += norm1(mixer(x)); x += norm2(ff(x)); x += side(x, token).  The sublayers read x itself.
 void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev, int p0, const RowBufs& B, cudaStream_t s) {
     const LayerSpec& S = cfg_.layers[(size_t)i];
@@ -727,12 +810,17 @@ void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev,
         latent_prep(cq, A.q_rank, L.dq_norm, S.kv_from < 0 ? dkv : nullptr, A.kv_rank, A.rot_dim, L.dkv_norm, eps, kcs_[(size_t)i], cache_dt_, S.rot.dims,
                     S.rot.interleaved, S.rot.base, T, pos_dev, p0, s);
         rows_matmul(q, cq, L.w_uq, T, s);
+        if (!pos_dev && latent_expand_ok(S, T)) {
+            latent_attention_rows(i, T, p0, q, o, s);
+            rows_matmul(B.y, o, L.wo, T, s);
+        } else {
         latent_q_absorb(qa, q, L.w_uk.ptr, L.w_uk.dtype, T, S.heads, S.dim, A.rot_dim, A.kv_rank, S.rot.dims, S.rot.interleaved, S.rot.base, pos_dev, p0, s);
         WindowAttn a;                       // one key / value head: keys are the whole cache rows, values their first kv_rank numbers
         a.heads = S.heads; a.kv_heads = 1; a.dim = row; a.vdim = A.kv_rank; a.scale = S.scale; a.k_stride = row; a.v_stride = row;
         attention_window(ol, qa, kcs_[(size_t)i], kcs_[(size_t)i], cache_dt_, T, pos_dev, p0, cfg_.max_seq_len, a, s);
         latent_v_up(o, ol, L.w_uv.ptr, L.w_uv.dtype, T, S.heads, S.vdim, A.kv_rank, s);
         rows_matmul(B.y, o, L.wo, T, s);
+        }
     } else {
         const ScanSpec& C = S.scan;
         const int inner = S.heads * S.vdim, ch = inner + 2 * C.groups * C.state, ld = inner + ch + S.heads;
@@ -763,10 +851,12 @@ void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev,
         } else {
             moe_route(pf_.sel, pf_.wt, nullptr, B.x, w, T, s);
             moe_group(pf_.work, pf_.sel, T, S.experts, S.top, s);
-            moe_expert_gate_rows(pf_.gate_rows, B.x, pf_.work, w, T, s);
-            moe_expert_up_rows(pf_.act_rows, B.x, pf_.work, w, T, s);
-            glu_bias_mul(pf_.act_rows, pf_.gate_rows, pf_.act_rows, nullptr, nullptr, T * S.top, S.ff, false, s);
-            moe_expert_down_rows(pf_.y_rows, pf_.act_rows, pf_.work, w, T, s);
+            if (S.act != GluAct::SILU || !moe_glu_rows_tc(i, T, B.x, s)) {
+                moe_expert_gate_rows(pf_.gate_rows, B.x, pf_.work, w, T, s);
+                moe_expert_up_rows(pf_.act_rows, B.x, pf_.work, w, T, s);
+                glu_bias_mul(pf_.act_rows, pf_.gate_rows, pf_.act_rows, nullptr, nullptr, T * S.top, S.ff, false, s);
+                moe_expert_down_rows(pf_.y_rows, pf_.act_rows, pf_.work, w, T, s);
+            }
             moe_combine(B.y, pf_.y_rows, pf_.work, pf_.wt, nullptr, nullptr, T, S.experts, S.top, hidden, s);
         }
         add_rmsnorm_rows(B.x, B.y, L.ffn_norm, nullptr, T, hidden, eps, s);

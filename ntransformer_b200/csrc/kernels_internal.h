@@ -247,6 +247,20 @@ void latent_q_absorb(float* qa, const float* q, const void* W_uk, DType dt, int 
                      bool interleaved, float rot_base, const int* pos_dev, int p0, cudaStream_t s);
 // ol [T, heads, kv_rank] -> out [T, heads * vdim] = W_uv,h ol_h;  W_uv [heads * vdim, kv_rank]
 void latent_v_up(float* out, const float* ol, const void* W_uv, DType dt, int T, int heads, int vdim, int kv_rank, cudaStream_t s);
+// Prompt portions: F32 latents of cache rows r0.. (input of the two up-projection GEMMs); their results packed with the rotated key part
+// into 16-bit per-head operands kfull [row, heads, kw] / vfull [row, heads, vw] (zero padded); queries rotated and padded to kw; the
+// padded outputs [T, heads, vw] back to [T, heads * vdim].
+void latent_rows_f32(float* out, const void* cache, DType cache_dt, int row, int kv_rank, int r0, int n, cudaStream_t s);
+void latent_expand_pack(void* kfull, void* vfull, const float* ku, const float* vu, const void* cache, DType cache_dt, int kv_rank, int r0, int n, int heads,
+                        int dim, int rot_dim, int vdim, int kw, int vw, cudaStream_t s);
+void latent_q_rot_pad(float* qp, const float* q, int T, int heads, int dim, int rot_dim, int kw, int rot_dims, bool interleaved, float rot_base, int p0,
+                      cudaStream_t s);
+void latent_unpad(float* out, const float* o, int T, int heads, int vdim, int vw, cudaStream_t s);
+// attention_prefill_mma.cu: full causal attention of `tokens` queries [tokens, heads, kw] at positions p0.. over BF16 per-head keys
+// [rows, heads, kw] and values [rows, heads, vw]; (kw, vw) from attention_heads_mma_widths.  out [tokens, heads, vw].
+bool attention_heads_mma_widths(int key_dim, int value_dim, int* kw, int* vw);
+void attention_heads_mma(float* out, const float* Q, const void* k, const void* v, int tokens, int p0, int rows, int heads, int kw, int vw, float scale,
+                         cudaStream_t s);
 // State-space scan (ScanSpec).  u [T, ld]: the input projection's rows; channels of interest start at a column offset.
 // conv_state [taps - 1, ch], state [heads, vdim, N]: the sequence's state, read unless the step starts at position 0, updated in place.
 void ssm_conv(float* out, const float* u, int ld, int col0, float* conv_state, const float* w, const float* b, int T, int ch, int taps,
@@ -281,6 +295,7 @@ inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
 size_t gemm_f16_tc_workspace_bytes(int M, int K);
 bool gemm_f16_tc(float* C, const float* A, const void* W_f16, int M, int N, int K, void* workspace, cudaStream_t s);
 bool gemm_f16_tc_supported(const void* W_f16, int N, int K, size_t row_pitch);
+bool gemm_f16_tc_ragged_supported(const void* W_f16, int N, int K, size_t row_pitch);   // gemm_f16_tc_ws alone: N >= 128, N % 4 == 0
 // Variants of the tensor-core GEMM: bf16 — weights and the activation split are BF16 (safetensors families; the same 16-bit
 // layouts, only the MMA's operand format changes); gelu — the gated epilogue uses tanh-GELU instead of SiLU; col_scale / alpha —
 // the store / add epilogue writes C (+)= alpha * col_scale[n] * (A.W^T) (per-channel layer scale and residual multiplier).

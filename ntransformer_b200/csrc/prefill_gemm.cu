@@ -266,6 +266,7 @@ __global__ void __launch_bounds__(192, 1) gemm_f16_tc_kernel(const __grid_consta
                         float* crow = C + (size_t)row * N + n0 + c * 32;
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
+                            if (n0 + c * 32 + j >= N) break;             // a ragged last tile (N % 4 == 0): TMA filled the missing weight rows with zeros
                             float4* dst = reinterpret_cast<float4*>(crow + j);
                             float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
                             if (col_scale || alpha != 1.0f) {           // C (+)= alpha * col_scale[n] * acc: layer scale and residual multiplier
@@ -352,6 +353,12 @@ bool gemm_f16_tc_supported(const void* W_f16, int N, int K, size_t row_pitch) {
            (reinterpret_cast<uintptr_t>(W_f16) & 15) == 0 && encode_fn() != nullptr;
 }
 
+// Store / add form only: the last column tile may be ragged (N >= 128, N % 4 == 0 so that the epilogue's 16-byte stores stay whole).
+bool gemm_f16_tc_ragged_supported(const void* W_f16, int N, int K, size_t row_pitch) {
+    return N >= 128 && K > 0 && N % 4 == 0 && K % BK == 0 && (row_pitch == 0 || row_pitch == (size_t)K * 2) &&
+           (reinterpret_cast<uintptr_t>(W_f16) & 15) == 0 && encode_fn() != nullptr;
+}
+
 // workspace <- F16 hi/lo split of A[M,K] (rows padded with zeros to a multiple of 128)
 void split_activations(void* workspace, const float* A, int M, int K, cudaStream_t s, bool bf16) {
     const size_t Mp = ((size_t)M + BM - 1) / BM * BM;
@@ -390,7 +397,7 @@ bool launch_gemm(float* C, __half* split_out, const void* workspace, const void*
         return false;
     static unsigned long long configured = 0;      // bit per device id
     opt_in_dynamic_smem(gemm_f16_tc_kernel<BN, MODE>, (int)(Cfg<BN>::SMEM), configured);
-    const int tiles_m = (int)(Mp / BM), tiles_n = N / TN, n_tiles = tiles_n * tiles_m;
+    const int tiles_m = (int)(Mp / BM), tiles_n = (N + TN - 1) / TN, n_tiles = tiles_n * tiles_m;
     const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     // Tile order: concurrently running CTAs share the operand that is walked in the inner loop, the other one should stay
     // L2-resident (126 MB) across the whole launch.  Keep the smaller operand resident: n-outer when the split activations
@@ -414,7 +421,7 @@ bool launch_gemm(float* C, __half* split_out, const void* workspace, const void*
 
 // C[M,N] (+)= split(A)[M,K] . W[N,K]^T with A already split into `workspace`
 bool gemm_f16_tc_ws(float* C, const void* workspace, const void* W_f16, int M, int N, int K, bool add, cudaStream_t s, const TcOpts& o) {
-    if (M <= 0 || !gemm_f16_tc_supported(W_f16, N, K, 0)) return false;
+    if (M <= 0 || !gemm_f16_tc_ragged_supported(W_f16, N, K, 0)) return false;
     const size_t Mp = ((size_t)M + BM - 1) / BM * BM;
     static const bool force128 = getenv("NT_B200_GEMM_BN128") != nullptr;
     if (N % 256 == 0 && !force128)

@@ -4,8 +4,9 @@
 //   ssm_conv_state   the state's update: the last taps - 1 inputs of [state ++ step rows]
 //   ssm_scan         per head h (group g = h / (heads / groups)), state S [state, vdim] in F32:
 //                        dt = softplus(dt_raw + dt_bias_h),  S <- exp(-exp(A_log_h) * dt) * S + dt * B_g x_h^T,  y_h = S^T C_g + D_h x_h
-//                    sequential over the step's rows, one warp per (head, value channel), lanes over the state dimension; the state is
-//                    read at the start (zeros at position 0) and written back at the end, so a prompt cut anywhere continues exactly
+//                    sequential over the step's rows; the state is read at the start (zeros at position 0) and written back at the
+//                    end, so a prompt cut anywhere continues exactly.  One decoded token: a warp per (head, value channel), lanes over
+//                    the state dimension.  Prompt rows: ssm_scan_rows_kernel below
 //   ssm_gate_norm    y * silu(z), RMS norm over each of `norm_groups` equal parts, times a gain
 // A step's base position is *pos_dev when given (the captured decode step), else p0.  Everything is F32.
 // Compiled WITHOUT --use_fast_math (expf / log1pf / division at full precision).
@@ -102,6 +103,100 @@ __global__ void __launch_bounds__(SC_WARPS * 32) ssm_scan_kernel(float* __restri
     for (int e = 0; e < NPL; e++) { const int n = lane + 32 * e; if (n < N) st[n] = S[e]; }
 }
 
+// Prompt rows.  A CTA owns 32 value channels of one head, 8 lanes per channel, NPT state elements per lane (lane l holds elements
+// 4 (l + 8 q) + j), so the 32 channels of a head share every B_t / C_t read as one broadcast 16-byte load.  The step's rows come through
+// shared memory in tiles of TT tokens (cp.async, two buffers): B and C of the head's group, the channels' x, the head's raw dt; softplus
+// and the decay's exponential are computed once per (token, head) when a tile lands, outside the serial chain.  The chain itself is
+// NPT multiply-adds for the state, NPT for y, and three shuffles per token.
+constexpr int SR_VB = 32;
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+template <int NPT>
+__global__ void __launch_bounds__(256) ssm_scan_rows_kernel(float* __restrict__ y, const float* __restrict__ xbc, int ch, const float* __restrict__ u, int ld,
+                                                            int dt_col0, float* __restrict__ state, const float* __restrict__ dt_bias,
+                                                            const float* __restrict__ A_log, const float* __restrict__ D, int T, int heads, int vdim,
+                                                            int N, int groups, int p0) {
+    constexpr int TT = NPT == 32 ? 8 : 16, NS = 8 * NPT, BUF = 2 * TT * NS + TT * SR_VB + TT;
+    extern __shared__ __align__(16) float sm[];
+    float* ysm = sm + 2 * BUF;             // [TT][SR_VB]
+    float* dd = ysm + TT * SR_VB;          // [2][TT]: dt, decay
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, v0 = blockIdx.x * SR_VB, g = h / (heads / groups);
+    const int pair = threadIdx.x >> 3, l = threadIdx.x & 7, v = v0 + pair;
+    const bool live = v < vdim;
+    const int inner = heads * vdim;
+    for (int e = threadIdx.x; e < 2 * BUF; e += 256) sm[e] = 0.f;          // the pad columns n >= N stay zero: cp.async never writes them
+    __syncthreads();
+    const float* Bp = xbc + inner + (size_t)g * N;
+    const float* Cp = Bp + (size_t)groups * N;
+    auto stage = [&](int k, int b) {
+        float* Bs = sm + b * BUF; float* Cs = Bs + TT * NS; float* xs = Cs + TT * NS; float* ds = xs + TT * SR_VB;
+        const int t0 = k * TT, nt = min(TT, T - t0);
+        for (int e = threadIdx.x; e < nt * N; e += 256) {
+            const int tt = e / N, n = e % N;
+            cp_async4(Bs + tt * NS + n, Bp + (size_t)(t0 + tt) * ch + n);
+            cp_async4(Cs + tt * NS + n, Cp + (size_t)(t0 + tt) * ch + n);
+        }
+        for (int e = threadIdx.x; e < nt * SR_VB; e += 256) {
+            const int tt = e / SR_VB, vv = e % SR_VB;
+            if (v0 + vv < vdim) cp_async4(xs + e, xbc + (size_t)(t0 + tt) * ch + (size_t)h * vdim + v0 + vv);
+        }
+        if (threadIdx.x < nt) cp_async4(ds + threadIdx.x, u + (size_t)(t0 + threadIdx.x) * ld + dt_col0 + h);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float S[NPT];
+    float* st = state + ((size_t)h * vdim + (live ? v : 0)) * N;
+#pragma unroll
+    for (int q = 0; q < NPT / 4; q++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const int n = 4 * (l + 8 * q) + j; S[4 * q + j] = (p0 != 0 && live && n < N) ? st[n] : 0.f; }
+    const float a_h = -expf(A_log[h]), bias = dt_bias[h], d_h = D[h];
+    const int n_tiles = (T + TT - 1) / TT;
+    stage(0, 0);
+    for (int k = 0; k < n_tiles; k++) {
+        const int b = k & 1, t0 = k * TT, nt = min(TT, T - t0);
+        if (k + 1 < n_tiles) { stage(k + 1, b ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float* Bs = sm + b * BUF; const float* Cs = Bs + TT * NS; const float* xs = Cs + TT * NS; const float* ds = xs + TT * SR_VB;
+        if (threadIdx.x < nt) {
+            const float dt = softplus_f(ds[threadIdx.x] + bias);
+            dd[threadIdx.x] = dt; dd[TT + threadIdx.x] = expf(a_h * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float dt = dd[tt], decay = dd[TT + tt];
+            const float x = live ? xs[tt * SR_VB + pair] : 0.f, dx = dt * x;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int q = 0; q < NPT / 4; q++) {
+                const float4 bv = *reinterpret_cast<const float4*>(Bs + tt * NS + 4 * (l + 8 * q));
+                const float4 cv = *reinterpret_cast<const float4*>(Cs + tt * NS + 4 * (l + 8 * q));
+                S[4 * q + 0] = fmaf(decay, S[4 * q + 0], dx * bv.x); part[0] = fmaf(S[4 * q + 0], cv.x, part[0]);
+                S[4 * q + 1] = fmaf(decay, S[4 * q + 1], dx * bv.y); part[1] = fmaf(S[4 * q + 1], cv.y, part[1]);
+                S[4 * q + 2] = fmaf(decay, S[4 * q + 2], dx * bv.z); part[2] = fmaf(S[4 * q + 2], cv.z, part[2]);
+                S[4 * q + 3] = fmaf(decay, S[4 * q + 3], dx * bv.w); part[3] = fmaf(S[4 * q + 3], cv.w, part[3]);
+            }
+            float p = (part[0] + part[1]) + (part[2] + part[3]);
+            p += __shfl_xor_sync(0xFFFFFFFFu, p, 1); p += __shfl_xor_sync(0xFFFFFFFFu, p, 2); p += __shfl_xor_sync(0xFFFFFFFFu, p, 4);
+            if (l == 0) ysm[tt * SR_VB + pair] = fmaf(d_h, x, p);
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * SR_VB; e += 256) {
+            const int tt = e / SR_VB, vv = e % SR_VB;
+            if (v0 + vv < vdim) y[(size_t)(t0 + tt) * inner + (size_t)h * vdim + v0 + vv] = ysm[e];
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int q = 0; q < NPT / 4; q++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) { const int n = 4 * (l + 8 * q) + j; if (n < N) st[n] = S[4 * q + j]; }
+    }
+}
+
 // grid (T, norm_groups); z = u[t, z_col0 + i]
 __global__ void __launch_bounds__(256) ssm_gate_norm_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ u, int ld, int z_col0,
                                                             const float* __restrict__ gain, float eps, int inner, int per) {
@@ -148,6 +243,17 @@ void ssm_scan(float* y, const float* xbc, const float* u, int ld, int dt_col0, f
     NT_CHECK(N >= 1 && N <= 32 * SC_NPL, "ssm_scan: state sizes up to 256 are covered");
     NT_CHECK(groups >= 1 && heads % groups == 0, "ssm_scan: heads must be a multiple of groups");
     const int ch = heads * vdim + 2 * groups * N;
+    static const bool no_rows = getenv("NT_B200_NO_SCAN_ROWS") != nullptr;
+    if (T > 1 && !pos_dev && !no_rows) {
+        const dim3 rgrid((vdim + SR_VB - 1) / SR_VB, heads);
+#define NT_SCAN_ROWS(NPT) do { constexpr int TT = NPT == 32 ? 8 : 16; \
+        launch_k(ssm_scan_rows_kernel<NPT>, rgrid, dim3(256), sizeof(float) * (2 * (2 * TT * 8 * NPT + TT * SR_VB + TT) + TT * SR_VB + 2 * TT), s, y, xbc, ch, u, ld, \
+                 dt_col0, state, dt_bias, A_log, D, T, heads, vdim, N, groups, p0); } while (0)
+        if (N <= 32) NT_SCAN_ROWS(4); else if (N <= 64) NT_SCAN_ROWS(8); else if (N <= 128) NT_SCAN_ROWS(16); else NT_SCAN_ROWS(32);
+#undef NT_SCAN_ROWS
+        count_launch();
+        return;
+    }
     const dim3 grid((heads * vdim + SC_WARPS - 1) / SC_WARPS);
 #define NT_SCAN(NPL) launch_k(ssm_scan_kernel<NPL>, grid, dim3(SC_WARPS * 32), 0, s, y, xbc, ch, u, ld, dt_col0, state, dt_bias, A_log, D, T, heads, vdim, N, groups, pos_dev, p0)
     if (N <= 32) NT_SCAN(1); else if (N <= 64) NT_SCAN(2); else if (N <= 128) NT_SCAN(4); else NT_SCAN(8);

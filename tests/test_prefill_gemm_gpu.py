@@ -68,6 +68,27 @@ def test_gemm_add_epilogue_and_many_tiles_per_cta(shape):
     assert (Cm.double() - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("shape", [(128, 132, 64), (70, 576, 256), (300, 1412, 512), (2048, 644, 128)])
+@pytest.mark.parametrize("add", [False, True])
+def test_gemm_ragged_last_column_tile(shape, add):
+    """N is a multiple of 4 but not of the tile width: the last column tile reads zero rows past the matrix and stores only the columns
+    that exist (the floats behind C stay as they were)."""
+    M, N, Kd = shape
+    g = torch.Generator(device="cuda").manual_seed(N * 3 + Kd)
+    A = torch.randn(M, Kd, device="cuda", generator=g)
+    W = (torch.randn(N, Kd, device="cuda", generator=g) * 0.05).half()
+    C0 = torch.randn(M * N + 4096, device="cuda", generator=g)
+    buf = C0.clone()
+    ws = torch.empty(K.gemm_f16_tc_workspace_bytes(M, Kd), dtype=torch.uint8, device="cuda")
+    K.split_activations(ws, A, M, Kd)
+    K.gemm_f16_tc_ws(buf, ws, W, M, N, Kd, add=add)
+    torch.cuda.synchronize()
+    ref = A.double() @ W.double().T + (C0[:M * N].view(M, N).double() if add else 0.0)
+    got = buf[:M * N].view(M, N).double()
+    assert (got - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+    assert torch.equal(buf[M * N:], C0[M * N:])
+
+
 @pytest.mark.parametrize("shape", [(128, 128, 64), (77, 1024, 512), (600, 14336, 4096)])
 def test_gemm_swiglu_epilogue_vs_torch_f64(shape):
     M, N, Kd = shape

@@ -60,17 +60,25 @@ def test_latent_rows_norms_rotation_and_cache_write(cache, q_rank, kv_rank, rot_
     assert torch.equal(CQ2, CQ) and torch.equal(before, kc)
 
 
-def latent_reference(q, rows, W_uk, W_uv, pos, H, D, R, V, kv_rank, dims, base, scale):
-    """One query row q [H * (D + R)] at position pos over cache rows [n, kv_rank + R] -> [H * V], keys and values expanded per head."""
+def round16(a):
+    return torch.tensor(a, dtype=torch.float32).to(torch.bfloat16).to(torch.float64).numpy()
+
+
+def latent_reference(q, rows, W_uk, W_uv, pos, H, D, R, V, kv_rank, dims, base, scale, rounded=False):
+    """One query row q [H * (D + R)] at position pos over cache rows [n, kv_rank + R] -> [H * V], keys and values expanded per head
+    (rounded: and kept in 16 bits, as the prompt-portion form keeps them)."""
     c, kr = rows[:pos + 1, :kv_rank], rows[:pos + 1, kv_rank:]
     out = np.zeros((H, V))
     for h in range(H):
         qh = q[h * (D + R):(h + 1) * (D + R)]
         qr = O.rotate_half(qh[None, D:], [pos], dims, base)[0] if dims else qh[D:]
         kn = c @ W_uk[h * D:(h + 1) * D].T
+        vals = c @ W_uv[h * V:(h + 1) * V].T
+        if rounded:
+            kn, vals = round16(kn), round16(vals)
         s = (kn @ qh[:D] + kr @ qr) * scale
         w = np.exp(s - s.max()); w /= w.sum()
-        out[h] = w @ (c @ W_uv[h * V:(h + 1) * V].T)
+        out[h] = w @ vals
     return out.reshape(-1)
 
 
@@ -123,6 +131,63 @@ def test_one_loud_key_among_a_thousand(T, far):
     np.testing.assert_allclose(got[-1], want, rtol=1e-4, atol=1e-4)
     ref = latent_reference(q[-1], rows, uk, uv, n - 1, H, D, R, V, kv_rank, 0, 10.0, 1.0)
     np.testing.assert_allclose(got[-1], ref, rtol=1e-4, atol=1e-4)
+
+
+def run_latent_expanded(q, rows_dev, W_uk, W_uv, T, p0, H, D, R, V, kv_rank, dims, base, scale):
+    out = torch.zeros(T, H * V, device="cuda")
+    rc = lib().nt_b200_latent_attention_expanded(out.data_ptr(), dev(q).data_ptr(), rows_dev.data_ptr(), W_uk.data_ptr(), W_uv.data_ptr(), int(DType.BF16), T, p0, H, D, R,
+                                                 V, kv_rank, dims, 0, base, scale, stream())
+    assert rc == 0
+    return host(out)
+
+
+@pytest.mark.parametrize("H,D,R,V,kv_rank,dims", [(3, 8, 6, 10, 20, 6), (1, 48, 16, 64, 64, 16), (2, 100, 28, 40, 72, 12), (2, 130, 62, 128, 96, 62), (2, 6, 0, 5, 9, 0),
+                                                  (4, 64, 64, 100, 32, 32)])
+def test_latent_attention_expanded_for_prompt_portions(H, D, R, V, kv_rank, dims):
+    """A prompt portion expands the rows it sees into per-head keys and values (rounded to 16 bits) and runs tiled attention over them:
+    the answers of a reference that rounds them the same way, and those of the form on the cached rows to that rounding; head widths are
+    padded to 64 / 128 / 192."""
+    rng = np.random.default_rng(H + D + V)
+    n, base, scale = 330, 50.0, (D + R) ** -0.5
+    rows_dev = dev(rng.standard_normal((n, kv_rank + R)), torch.bfloat16)
+    W_uk = dev(rng.standard_normal((H * D, kv_rank)) * kv_rank ** -0.5, torch.bfloat16); W_uv = dev(rng.standard_normal((H * V, kv_rank)) * kv_rank ** -0.5, torch.bfloat16)
+    rows, uk, uv = host(rows_dev), host(W_uk), host(W_uv)
+    for p0, T in ((0, n), (37, 20), (300, 16), (63, 66), (0, 17)):
+        q = rng.standard_normal((T, H * (D + R)))
+        got = run_latent_expanded(q, rows_dev, W_uk, W_uv, T, p0, H, D, R, V, kv_rank, dims, base, scale)
+        ref = np.stack([latent_reference(q[t], rows, uk, uv, p0 + t, H, D, R, V, kv_rank, dims, base, scale, rounded=True) for t in range(T)])
+        assert rel_rms(got, ref) < 1e-3            # a key or value that sits within F32 rounding of a 16-bit tie may round the other way
+        plain = np.stack([latent_reference(q[t], rows, uk, uv, p0 + t, H, D, R, V, kv_rank, dims, base, scale) for t in range(T)])
+        assert rel_rms(got, plain) < 1.5e-2
+
+
+def test_expanded_form_refuses_what_it_does_not_cover():
+    z = torch.zeros(16, device="cuda")
+    for T, D, R, V in ((8, 8, 8, 8), (16, 150, 50, 64), (16, 32, 32, 130)):
+        assert lib().nt_b200_latent_attention_expanded(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), int(DType.BF16), T, 0, 1, D, R, V, 16, 0, 0,
+                                                       10.0, 1.0, stream()) == -1
+
+
+@pytest.mark.parametrize("far", [0, 1, 62, 63, 64, 65, 127, 128, 700, 935, 936, 998, 999])
+def test_one_loud_key_in_a_prompt_portion(far):
+    """The expanded form walks 64-key tiles: a row made to match the last query is found in the first tile, at tile borders, in the
+    tile that holds the portion's first query, and at the query's own place."""
+    rng = np.random.default_rng(far)
+    H, D, R, V, kv_rank, n, T = 2, 8, 4, 6, 16, 1000, 64
+    rows = rng.standard_normal((n, kv_rank + R)) * 0.1
+    uk = np.zeros((H * D, kv_rank)); uv = rng.standard_normal((H * V, kv_rank))
+    for h in range(H):
+        uk[h * D:(h + 1) * D, :D] = np.eye(D)
+    rows[far, :D] = 3.0
+    q = rng.standard_normal((T, H * (D + R))) * 0.1
+    q[-1] = 0.0
+    for h in range(H):
+        q[-1, h * (D + R):h * (D + R) + D] = 4.0
+    rows_dev, W_uk, W_uv = dev(rows, torch.bfloat16), dev(uk, torch.bfloat16), dev(uv, torch.bfloat16)
+    got = run_latent_expanded(q, rows_dev, W_uk, W_uv, T, n - T, H, D, R, V, kv_rank, 0, 10.0, 1.0)
+    ref = latent_reference(q[-1], host(rows_dev), host(W_uk), host(W_uv), n - 1, H, D, R, V, kv_rank, 0, 10.0, 1.0)
+    np.testing.assert_allclose(got[-1], ref, rtol=2e-2, atol=2e-2)
+    assert np.abs(ref - host(rows_dev)[far, :kv_rank] @ host(W_uv).T).max() < 1e-3       # the reference itself sits on that row
 
 
 @pytest.mark.parametrize("taps,ch", [(4, 37), (1, 5), (2, 300), (7, 12)])
@@ -346,9 +411,10 @@ def test_model_schedules_agree_with_oracle(name, exact):
     def close(got):
         if exact:
             return rel_rms(got, ref) < 3e-4
-        # 16-bit cache rows, and a choice score within rounding of the next one may pick the other expert at a position
+        # 16-bit cache rows and expanded keys / values; a choice score within rounding of the next one may pick the other expert at a
+        # position: a few isolated positions may be far off, the rest not
         err = per_position(got, ref)
-        return np.median(err) < 1.5e-2 and err.max() < 0.25
+        return np.median(err) < 1.5e-2 and np.sort(err)[-3] < 0.05 and (err > 0.25).sum() <= 2
 
     whole = run_portions(m, toks, [S])
     assert close(whole)
@@ -402,6 +468,27 @@ def test_rows_and_state_are_reused_between_requests():
         assert rel_rms(alone, O.forward(cfg, W, b)) < 2e-4
         after_a = run_portions(m, b[:3], [1, 1, 1])                      # and again, decoding from the very first token
         np.testing.assert_array_equal(after_a, run_portions(m2, b[:3], [1, 1, 1]))
+
+
+def test_prompt_longer_than_one_portion_and_one_block_of_expanded_rows():
+    """2100 tokens: the engine cuts the prompt after 2048, the second portion expands the rows before it in two blocks, and the scan's
+    state and convolution inputs cross the cut; then the same prompt in uneven portions, and tokens decoded behind it."""
+    rng = np.random.default_rng(21)
+    cfg, W = O.random_model(rng, pattern=("latent", "scan", "latent"), kv_from={2: 0}, mlp=("dense", None, "moe"), width=32, vocab=50, state=40, s_vdim=33)
+    S = 2100
+    toks = rng.integers(0, cfg["vocab"], S).astype(np.int32)
+    ref = O.forward(cfg, W, toks)
+    m = build(cfg, W, False, max_context=2304)
+    want = [0, 1, 15, 16, 63, 64, 1000, 2046, 2047, 2048, 2049, 2063, 2064] + list(range(2080, S))
+    got = m.forward_logits(toks, 0, want)
+    err = per_position(got, ref[want])
+    assert np.median(err) < 1.5e-2 and np.sort(err)[-3] < 0.05, (np.median(err), err.max())
+    m.clear_kv()
+    cuts = [1000, 700, 17, 300, 2, 61, 16, 4]
+    got2 = run_portions(m, toks, cuts)
+    err2 = per_position(got2[want], ref[want])
+    assert np.median(err2) < 1.5e-2 and np.sort(err2)[-3] < 0.05, (np.median(err2), err2.max())
+    m.close()
 
 
 def test_long_decode_and_graph_replay():
