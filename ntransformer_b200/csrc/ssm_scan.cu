@@ -13,6 +13,7 @@
 #include "kernels_internal.h"
 #include "ring.cuh"
 #include <algorithm>
+#include <cstdint>
 
 namespace nt { namespace b200 {
 
@@ -103,43 +104,57 @@ __global__ void __launch_bounds__(SC_WARPS * 32) ssm_scan_kernel(float* __restri
     for (int e = 0; e < NPL; e++) { const int n = lane + 32 * e; if (n < N) st[n] = S[e]; }
 }
 
-// Prompt rows.  A CTA owns 32 value channels of one head, 8 lanes per channel, NPT state elements per lane (lane l holds elements
-// 4 (l + 8 q) + j), so the 32 channels of a head share every B_t / C_t read as one broadcast 16-byte load.  The step's rows come through
+// Prompt rows.  A CTA owns VB (32, or 16 when that is what fills the SMs) value channels of one head, LN (8 or 16) lanes per channel,
+// NPT state elements per lane (lane l holds elements 4 (l + LN q) + j), so the channels of a warp share every B_t / C_t read as one
+// broadcast 16-byte load.  The kernel is bound by instruction latency (one to two warps per scheduler), so states of 64 and more take
+// 16 lanes per channel: twice the warps, half the chain per lane.  The step's rows come through
 // shared memory in tiles of TT tokens (cp.async, two buffers): B and C of the head's group, the channels' x, the head's raw dt; softplus
 // and the decay's exponential are computed once per (token, head) when a tile lands, outside the serial chain.  The chain itself is
 // NPT multiply-adds for the state, NPT for y, and three shuffles per token.
-constexpr int SR_VB = 32;
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
-template <int NPT>
-__global__ void __launch_bounds__(256) ssm_scan_rows_kernel(float* __restrict__ y, const float* __restrict__ xbc, int ch, const float* __restrict__ u, int ld,
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+template <int NPT, int SR_VB, int LN>
+__global__ void __launch_bounds__(SR_VB * LN) ssm_scan_rows_kernel(float* __restrict__ y, const float* __restrict__ xbc, int ch, const float* __restrict__ u, int ld,
                                                             int dt_col0, float* __restrict__ state, const float* __restrict__ dt_bias,
                                                             const float* __restrict__ A_log, const float* __restrict__ D, int T, int heads, int vdim,
                                                             int N, int groups, int p0) {
-    constexpr int TT = NPT == 32 ? 8 : 16, NS = 8 * NPT, BUF = 2 * TT * NS + TT * SR_VB + TT;
+    constexpr int TT = LN * NPT > 128 ? 8 : 16, NS = LN * NPT, BUF = 2 * TT * NS + TT * SR_VB + TT;
     extern __shared__ __align__(16) float sm[];
     float* ysm = sm + 2 * BUF;             // [TT][SR_VB]
     float* dd = ysm + TT * SR_VB;          // [2][TT]: dt, decay
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y, v0 = blockIdx.x * SR_VB, g = h / (heads / groups);
-    const int pair = threadIdx.x >> 3, l = threadIdx.x & 7, v = v0 + pair;
+    const int pair = threadIdx.x / LN, l = threadIdx.x % LN, v = v0 + pair;
     const bool live = v < vdim;
     const int inner = heads * vdim;
-    for (int e = threadIdx.x; e < 2 * BUF; e += 256) sm[e] = 0.f;          // the pad columns n >= N stay zero: cp.async never writes them
+    for (int e = threadIdx.x; e < 2 * BUF; e += SR_VB * LN) sm[e] = 0.f;          // the pad columns n >= N stay zero: cp.async never writes them
     __syncthreads();
     const float* Bp = xbc + inner + (size_t)g * N;
     const float* Cp = Bp + (size_t)groups * N;
+    const bool vec = ((N | ch | inner) & 3) == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
     auto stage = [&](int k, int b) {
         float* Bs = sm + b * BUF; float* Cs = Bs + TT * NS; float* xs = Cs + TT * NS; float* ds = xs + TT * SR_VB;
         const int t0 = k * TT, nt = min(TT, T - t0);
-        for (int e = threadIdx.x; e < nt * N; e += 256) {
-            const int tt = e / N, n = e % N;
-            cp_async4(Bs + tt * NS + n, Bp + (size_t)(t0 + tt) * ch + n);
-            cp_async4(Cs + tt * NS + n, Cp + (size_t)(t0 + tt) * ch + n);
+        if (vec) {                                          // 16-byte copies: N, the row stride and the B / C offsets are multiples of 4 floats
+            const int n4 = N >> 2;
+            for (int e = threadIdx.x; e < nt * n4; e += SR_VB * LN) {
+                const int tt = e / n4, n = (e - tt * n4) << 2;
+                cp_async16(Bs + tt * NS + n, Bp + (size_t)(t0 + tt) * ch + n);
+                cp_async16(Cs + tt * NS + n, Cp + (size_t)(t0 + tt) * ch + n);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * N; e += SR_VB * LN) {
+                const int tt = e / N, n = e % N;
+                cp_async4(Bs + tt * NS + n, Bp + (size_t)(t0 + tt) * ch + n);
+                cp_async4(Cs + tt * NS + n, Cp + (size_t)(t0 + tt) * ch + n);
+            }
         }
-        for (int e = threadIdx.x; e < nt * SR_VB; e += 256) {
+        for (int e = threadIdx.x; e < nt * SR_VB; e += SR_VB * LN) {
             const int tt = e / SR_VB, vv = e % SR_VB;
             if (v0 + vv < vdim) cp_async4(xs + e, xbc + (size_t)(t0 + tt) * ch + (size_t)h * vdim + v0 + vv);
         }
@@ -151,7 +166,7 @@ __global__ void __launch_bounds__(256) ssm_scan_rows_kernel(float* __restrict__ 
 #pragma unroll
     for (int q = 0; q < NPT / 4; q++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) { const int n = 4 * (l + 8 * q) + j; S[4 * q + j] = (p0 != 0 && live && n < N) ? st[n] : 0.f; }
+        for (int j = 0; j < 4; j++) { const int n = 4 * (l + LN * q) + j; S[4 * q + j] = (p0 != 0 && live && n < N) ? st[n] : 0.f; }
     const float a_h = -expf(A_log[h]), bias = dt_bias[h], d_h = D[h];
     const int n_tiles = (T + TT - 1) / TT;
     stage(0, 0);
@@ -166,25 +181,39 @@ __global__ void __launch_bounds__(256) ssm_scan_rows_kernel(float* __restrict__ 
             dd[threadIdx.x] = dt; dd[TT + threadIdx.x] = expf(a_h * dt);
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; tt++) {
+        float yv[TT];                                       // this channel's outputs of the tile: stored behind the loop, so that no shared
+                                                            // store stands between one token's loads and the next one's
+        auto step = [&](int tt) {
             const float dt = dd[tt], decay = dd[TT + tt];
             const float x = live ? xs[tt * SR_VB + pair] : 0.f, dx = dt * x;
             float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int q = 0; q < NPT / 4; q++) {
-                const float4 bv = *reinterpret_cast<const float4*>(Bs + tt * NS + 4 * (l + 8 * q));
-                const float4 cv = *reinterpret_cast<const float4*>(Cs + tt * NS + 4 * (l + 8 * q));
+                const float4 bv = *reinterpret_cast<const float4*>(Bs + tt * NS + 4 * (l + LN * q));
+                const float4 cv = *reinterpret_cast<const float4*>(Cs + tt * NS + 4 * (l + LN * q));
                 S[4 * q + 0] = fmaf(decay, S[4 * q + 0], dx * bv.x); part[0] = fmaf(S[4 * q + 0], cv.x, part[0]);
                 S[4 * q + 1] = fmaf(decay, S[4 * q + 1], dx * bv.y); part[1] = fmaf(S[4 * q + 1], cv.y, part[1]);
                 S[4 * q + 2] = fmaf(decay, S[4 * q + 2], dx * bv.z); part[2] = fmaf(S[4 * q + 2], cv.z, part[2]);
                 S[4 * q + 3] = fmaf(decay, S[4 * q + 3], dx * bv.w); part[3] = fmaf(S[4 * q + 3], cv.w, part[3]);
             }
             float p = (part[0] + part[1]) + (part[2] + part[3]);
-            p += __shfl_xor_sync(0xFFFFFFFFu, p, 1); p += __shfl_xor_sync(0xFFFFFFFFu, p, 2); p += __shfl_xor_sync(0xFFFFFFFFu, p, 4);
-            if (l == 0) ysm[tt * SR_VB + pair] = fmaf(d_h, x, p);
+            #pragma unroll
+            for (int o = 1; o < LN; o <<= 1) p += __shfl_xor_sync(0xFFFFFFFFu, p, o);
+            return fmaf(d_h, x, p);
+        };
+        if (nt == TT) {
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) yv[tt] = step(tt);       // independent loads and reductions of neighbouring tokens overlap; only S is carried
+        } else {
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) if (tt < nt) yv[tt] = step(tt);
+        }
+        if (l == 0) {
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) if (tt < nt) ysm[tt * SR_VB + pair] = yv[tt];
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < nt * SR_VB; e += 256) {
+        for (int e = threadIdx.x; e < nt * SR_VB; e += SR_VB * LN) {
             const int tt = e / SR_VB, vv = e % SR_VB;
             if (v0 + vv < vdim) y[(size_t)(t0 + tt) * inner + (size_t)h * vdim + v0 + vv] = ysm[e];
         }
@@ -193,7 +222,7 @@ __global__ void __launch_bounds__(256) ssm_scan_rows_kernel(float* __restrict__ 
 #pragma unroll
         for (int q = 0; q < NPT / 4; q++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) { const int n = 4 * (l + 8 * q) + j; if (n < N) st[n] = S[4 * q + j]; }
+            for (int j = 0; j < 4; j++) { const int n = 4 * (l + LN * q) + j; if (n < N) st[n] = S[4 * q + j]; }
     }
 }
 
@@ -245,12 +274,15 @@ void ssm_scan(float* y, const float* xbc, const float* u, int ld, int dt_col0, f
     const int ch = heads * vdim + 2 * groups * N;
     static const bool no_rows = getenv("NT_B200_NO_SCAN_ROWS") != nullptr;
     if (T > 1 && !pos_dev && !no_rows) {
-        const dim3 rgrid((vdim + SR_VB - 1) / SR_VB, heads);
-#define NT_SCAN_ROWS(NPT) do { constexpr int TT = NPT == 32 ? 8 : 16; \
-        launch_k(ssm_scan_rows_kernel<NPT>, rgrid, dim3(256), sizeof(float) * (2 * (2 * TT * 8 * NPT + TT * SR_VB + TT) + TT * SR_VB + 2 * TT), s, y, xbc, ch, u, ld, \
-                 dt_col0, state, dt_bias, A_log, D, T, heads, vdim, N, groups, p0); } while (0)
-        if (N <= 32) NT_SCAN_ROWS(4); else if (N <= 64) NT_SCAN_ROWS(8); else if (N <= 128) NT_SCAN_ROWS(16); else NT_SCAN_ROWS(32);
+        const bool narrow = vdim <= 16 || heads * ((vdim + 31) / 32) < 148;       // 16 channels per CTA: twice the CTAs
+#define NT_SCAN_ROWS_V(NPT, VB, LN) do { constexpr int TT = LN * NPT > 128 ? 8 : 16; \
+        launch_k(ssm_scan_rows_kernel<NPT, VB, LN>, dim3((vdim + VB - 1) / VB, heads), dim3(VB * LN), \
+                 sizeof(float) * (2 * (2 * TT * LN * NPT + TT * VB + TT) + TT * VB + 2 * TT), \
+                 s, y, xbc, ch, u, ld, dt_col0, state, dt_bias, A_log, D, T, heads, vdim, N, groups, p0); } while (0)
+#define NT_SCAN_ROWS(NPT, LN) do { if (narrow) NT_SCAN_ROWS_V(NPT, 16, LN); else NT_SCAN_ROWS_V(NPT, 32, LN); } while (0)
+        if (N <= 32) NT_SCAN_ROWS(4, 8); else if (N <= 64) NT_SCAN_ROWS(4, 16); else if (N <= 128) NT_SCAN_ROWS(8, 16); else NT_SCAN_ROWS(16, 16);
 #undef NT_SCAN_ROWS
+#undef NT_SCAN_ROWS_V
         count_launch();
         return;
     }
