@@ -805,8 +805,13 @@ void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev,
         const LatentSpec& A = S.latent;
         const int row = A.kv_rank + A.rot_dim;
         float *cq = B.t[0], *dkv = B.t[1], *q = B.t[2], *qa = B.t[3], *ol = B.t[4], *o = B.t[2];
-        rows_matmul(cq, B.x, L.w_dq, T, s);
-        if (S.kv_from < 0) rows_matmul(dkv, B.x, L.w_dkv, T, s);
+        if (T == 1 && S.kv_from < 0) {                  // one decoded token: both down-projections read x, one launch
+            GemvMat two[2] = {mat_of(L.w_dq, cq), mat_of(L.w_dkv, dkv)};
+            gemv_dense(two, 2, hidden, B.x, DENSE_STORE, nullptr, 1.f, s);
+        } else {
+            rows_matmul(cq, B.x, L.w_dq, T, s);
+            if (S.kv_from < 0) rows_matmul(dkv, B.x, L.w_dkv, T, s);
+        }
         latent_prep(cq, A.q_rank, L.dq_norm, S.kv_from < 0 ? dkv : nullptr, A.kv_rank, A.rot_dim, L.dkv_norm, eps, kcs_[(size_t)i], cache_dt_, S.rot.dims,
                     S.rot.interleaved, S.rot.base, T, pos_dev, p0, s);
         rows_matmul(q, cq, L.w_uq, T, s);
@@ -834,8 +839,13 @@ void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev,
     add_rmsnorm_rows(B.x, B.y, L.attn_norm, nullptr, T, hidden, eps, s);
     if (S.ff > 0 && S.ff_kind == FfKind::GLU) {
         float *g = B.t[0], *up = B.t[1];
-        rows_matmul(g, B.x, L.gate, T, s);
-        rows_matmul(up, B.x, L.up, T, s);
+        if (T == 1) {
+            GemvMat two[2] = {mat_of(L.gate, g), mat_of(L.up, up)};
+            gemv_dense(two, 2, hidden, B.x, DENSE_STORE, nullptr, 1.f, s);
+        } else {
+            rows_matmul(g, B.x, L.gate, T, s);
+            rows_matmul(up, B.x, L.up, T, s);
+        }
         glu_bias_mul(g, g, up, L.gate_b, L.up_b, T, S.ff, S.act == GluAct::GELU_TANH, s);
         rows_matmul(B.y, g, L.down, T, s);
         add_rmsnorm_rows(B.x, B.y, L.ffn_norm, L.down_b, T, hidden, eps, s);
