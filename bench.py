@@ -481,7 +481,7 @@ def cpu_baseline(model, cfg, mix, world):
 
     def timed(k, min_s):
         """fastest of >= 3 calls (a fixed amount of work per call): host-core contention from other tenants only ever adds time,
-        so the minimum is the stable figure (the mean swung 5x between driver runs in round 1)"""
+        so the minimum is the stable figure (the mean swung 5x between runs)"""
         om.forward([5], 0, n_layers_run=k)                       # warm page cache / thread pool
         t_all, best, reps = time.perf_counter(), float("inf"), 0
         while reps < 3 or time.perf_counter() - t_all < min_s:

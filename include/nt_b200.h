@@ -2,9 +2,9 @@
  * nt_b200.h — C-ABI of the B200-native resident-decode kernels (libnt_b200.so).
  *
  * Drop-in boundary: every entry point below replaces one launcher of the reference's
- * kernel interface  /root/reference/src/cuda/kernels.h:10-74  (C++ free functions in
+ * kernel interface  src/cuda/kernels.h:10-74  (C++ free functions in
  * namespace nt::cuda) or one of its extern "C" memory helpers
- * /root/reference/src/core/device.h:79-88.  Same argument order, meaning, units and
+ * src/core/device.h:79-88.  Same argument order, meaning, units and
  * (absence of) error reporting as the reference; `dtype` carries the numeric value of
  * nt::DType (reference src/core/types.h:24-35: F32 0, F16 1, Q8_0 2, Q4_0 3, Q4_K_M 4,
  * Q6_K 5, Q5_K 6); `stream` is a cudaStream_t passed as void*.  All pointers are DEVICE

@@ -1,6 +1,6 @@
 """Builds libnt_b200.so (CUDA kernels + C-ABI + native engine) in-tree with nvcc for sm_100a.
 
-The .so is git-ignored but travels to the GPU box with the gpurun snapshot. Incremental: a source is
+The .so is git-ignored and is built in-tree, so that it travels with a copy of the working tree. Incremental: a source is
 recompiled only when it (or a header) is newer than its object file.
 """
 from __future__ import annotations

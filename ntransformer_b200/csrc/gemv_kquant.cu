@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS <= 6 ? 2 : 1) gemv_kq_kernel
     }
 }
 
-// Q4_0 (reference K1, gemm.cu:32-86) runs on this path by default since its first hardware run (round 2: tests/test_q4_0_tma_gpu.py
+// Q4_0 (reference K1, gemm.cu:32-86) runs on this path by default since its first hardware run (tests/test_q4_0_tma_gpu.py
 // against the oracle, <= 2e-5); NT_B200_Q4_0_TMA=0 sends it back to the generic kernel (gemv_generic.cu) for A/B comparisons.
 bool q4_0_tma_enabled() {
     static const bool on = [] { const char* e = getenv("NT_B200_Q4_0_TMA"); return !(e && e[0] == '0' && e[1] == 0); }();

@@ -12,7 +12,7 @@
 //     divisions as the reference loops; exp() is evaluated in double and rounded to float, which reproduces glibc's
 //     (correctly rounded in practice) expf where the fast-math ex2.approx path would not;
 //   * the uniform variate r comes from the host's std::mt19937 exactly as in the reference (Sampler::draw in engine/text.cpp).
-// STATUS: written after round 1's GPU budget was spent; verified on the CPU emulator (tests/cusim, tests/test_sample_sim.py)
+// STATUS: first written without hardware access; verified on the CPU emulator (tests/cusim, tests/test_sample_sim.py)
 // against the reference's own sampler; opt-in (GenerateConfig::gpu_sampler / NT_B200_GPU_SAMPLER=1) until it has run on hardware.
 #include "kernels_internal.h"
 #include <cstdint>

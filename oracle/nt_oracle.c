@@ -2,7 +2,7 @@
  * nt_oracle.c — CPU restatement of the reference's resident decode path.
  * TEST INFRASTRUCTURE ONLY (see nt_oracle.h).  Plain C + OpenMP.
  *
- * Citations are file:line under /root/reference.
+ * Citations are file:line inside the reference project.
  */
 #include "nt_oracle.h"
 

@@ -6,7 +6,7 @@
  * and bench.py's cpu_baseline / --impl reference legs (as the checker or the
  * reported CPU baseline, never as the thing shipped).
  *
- * Every function cites the reference file:line (relative to /root/reference)
+ * Every function cites the reference file:line (relative to the reference project's root)
  * whose arithmetic it restates.  Dot products and reductions accumulate in
  * double: the reference accumulates the same products in F32 in a lane-strided
  * order (src/cuda/gemm.cu), so this restatement sits inside F32 rounding of any

@@ -1,4 +1,4 @@
-"""The decode chain's fusions (round 2) against the oracle, through the C-ABI:
+"""The decode chain's fusions against the oracle, through the C-ABI:
   * nt_b200_attention_decode_fused = launch_rope + launch_copy_to_kv_cache + launch_attention_decode in one launch
     (reference rotary.cu:16-62, attention.cu:316-342, attention.cu:108-202);
   * nt_b200_gemv_fused_f32 = RMSNorm + activation quantiser + GEMV in one launch

@@ -1,7 +1,7 @@
 """Opt-in GEMV kernel variants against the oracle (their switches are read once per process, hence the subprocesses):
   NT_B200_GEMV_QB=1      the quarter-block kernel (csrc/gemv_kquant_q.cu: lane <-> 64 weights, 16 warps) — measured slower than the
                          default half-block kernel (profiles/r02_qb_layer_ncu_summary.txt), kept as an A/B aid;
-  NT_B200_TAIL_SPLIT=0   whole 4-row stages in a partly filled last round (the pre-round-2 schedule)."""
+  NT_B200_TAIL_SPLIT=0   whole 4-row stages in a partly filled last round (the earlier schedule)."""
 import os
 import subprocess
 import sys

@@ -1,6 +1,6 @@
 """GPU parity of the persistent decode kernel (csrc/engine/decode_mega.h) against the verified graph path and the CPU oracle.
 
-First hardware run: round 2 (all single-GPU cases green on a B200).  The persistent kernel stays an opt-in decode path
+All single-GPU cases are green on a B200.  The persistent kernel stays an opt-in decode path
 (NT_B200_MEGAKERNEL=1 / nt_model_use_megakernel) because it is correct but slower than the graph of fused launches
 (profiles/r02_mega_*); these tests keep it correct.
 
@@ -67,7 +67,7 @@ def test_compat_mode_matches_graph_path(case, monkeypatch):
     cfg, mix, path, _ = case
     prompt = [cfg.bos_token_id, 17, 300, 5, 44, 9, 12, 400]
     # the persistent kernel's phases are transplants of the UNFUSED launch sequence (rmsnorm_xq -> GEMV over xq ...): compare with that
-    # form of the graph path (NT_B200_FUSE=0), not with the round-2 chain that moves the norm factor across the GEMV
+    # form of the graph path (NT_B200_FUSE=0), not with the fused chain that moves the norm factor across the GEMV
     monkeypatch.setenv("NT_B200_FUSE", "0")
     g = Model.load(path, cfg.max_seq_len)
     want, ids_g = run(g, prompt, 40)
@@ -83,7 +83,7 @@ def test_compat_mode_matches_graph_path(case, monkeypatch):
     worst = max(rel(a, b) for a, b in zip(got, want))
     exact = all(np.array_equal(a, b) for a, b in zip(got, want))
     print(f"{mix}: max rel diff vs graph path {worst:.3e}, bit-identical: {exact}")
-    assert worst <= 1e-4          # same slices, same per-slice arithmetic; the graph path's merge kernel adds the slices in another order since round 2
+    assert worst <= 1e-4          # same slices, same per-slice arithmetic; the graph path's merge kernel adds the slices in another order
     assert ids_m == ids_g
 
 

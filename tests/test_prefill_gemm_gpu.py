@@ -30,7 +30,7 @@ def test_gemm_f16_tc_vs_torch_f64(shape):
     torch.cuda.synchronize()
     ref = A.double() @ W.double().T
     err = (Cm.double() - ref).abs().max().item()
-    # K-chunked accumulation (4096 elements per fresh TMEM accumulator, partial sums added in F32 RN): round 1's single
+    # K-chunked accumulation (4096 elements per fresh TMEM accumulator, partial sums added in F32 RN): a single
     # accumulator measured 4e-5 at K = 14336 (tensor cores truncate once per MMA step); chunked it stays below 2.5e-5
     assert err <= 2.5e-5 * ref.abs().max().item(), (err, ref.abs().max().item())
 

@@ -1,4 +1,4 @@
-"""Q4_0 on the TMA/dp4a GEMV path (the default since round 2; process_stage<4> in csrc/gemv_kq_device.cuh) against the oracle,
+"""Q4_0 on the TMA/dp4a GEMV path (the default; process_stage<4> in csrc/gemv_kq_device.cuh) against the oracle,
 and the generic kernel (NT_B200_Q4_0_TMA=0) as the A/B twin.  The switch is read once per process, hence the subprocesses."""
 import os
 import subprocess

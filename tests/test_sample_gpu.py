@@ -1,6 +1,6 @@
 """GPU sampler (csrc/sample.cu, nt_model_sample) against the host sampler on the same logits, settings and mt19937 stream.
 
-First hardware run: round 2 (green); the sampler is the default of Engine::generate since.  Its logic is also verified on the
+Green on hardware; the sampler is the default of Engine::generate since.  Its logic is also verified on the
 CPU emulator against the reference's own sampler (tests/test_sample_sim.py).  On hardware the only expected
 difference is exp(): double-precision exp rounded to float vs glibc expf — identical draws except when r falls within an ulp
 of a CDF step, hence the >= 97 % bar below instead of equality."""
