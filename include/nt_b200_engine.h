@@ -88,6 +88,9 @@ int nt_b200_latent_attention_expanded(float* out, const float* q, const void* ca
 /* full causal attention over ONE key / value head stored as rows of `row` numbers: keys the first dim, values the first vdim of a row */
 void nt_b200_attention_rows(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,
                             int max_seq, void* stream);
+/* the same with all heads served from one shared-memory copy of the rows; -1: shape not covered (dim, row multiples of 16 bytes, heads <= 32, even vdim <= 512) */
+int nt_b200_attention_rows_shared(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,
+                                  int max_seq, void* stream);
 /* state-space scan: causal convolution + SiLU with a carried state, the recurrence with a carried state, gate + grouped RMS norm */
 void nt_b200_ssm_conv(float* out, const float* u, int ld, int col0, float* conv_state, const float* w, const float* b, int tokens, int ch, int taps, int p0, void* stream);
 void nt_b200_ssm_scan(float* y, const float* xbc, const float* u, int ld, int dt_col0, float* state, const float* dt_bias, const float* A_log, const float* D,

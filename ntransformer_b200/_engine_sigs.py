@@ -76,6 +76,7 @@ ENGINE_SIGNATURES = {
     "nt_b200_latent_q_absorb": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "nt_b200_latent_v_up": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "nt_b200_latent_attention_expanded": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "nt_b200_attention_rows_shared": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "nt_b200_attention_rows": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "nt_b200_ssm_conv": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "nt_b200_ssm_scan": (None, [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

@@ -22,6 +22,9 @@
 #include <cuda_fp16.h>
 #include <algorithm>
 #include <cmath>
+#include <cfloat>
+#include <cstdint>
+#include <cstdlib>
 
 namespace nt { namespace b200 {
 
@@ -91,34 +94,46 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(float* __restrict__ cq
 
 constexpr int LT = 8;      // tokens per CTA in the two per-head products
 
-// grid (ceil(T / LT), heads).  q [T, heads, dim + rot_dim]; qa [T, heads, kv_rank + rot_dim]; W_uk [heads * dim, kv_rank]
+// grid (ceil(T / LT), heads, ceil(kv_rank / 64)).  q [T, heads, dim + rot_dim]; qa [T, heads, kv_rank + rot_dim]; W_uk [heads * dim, kv_rank].
+// A CTA owns 64 latent channels of a head: thread (r, part) sums every fourth row of W_uk,h for channel r, the four parts meet in
+// shared memory.  One decoded token then has heads * kv_rank / 64 CTAs with short chains instead of `heads` CTAs with long ones.
 template <typename WT>
 __global__ void __launch_bounds__(256) latent_q_absorb_kernel(float* __restrict__ qa, const float* __restrict__ q, const WT* __restrict__ W_uk, int T, int heads,
                                                               int dim, int rot_dim, int kv_rank, int dims, int interleaved, double log2_base,
                                                               const int* __restrict__ pos_dev, int p0) {
-    extern __shared__ __align__(16) float qs[];           // [LT][dim + rot_dim]
+    extern __shared__ __align__(16) float qs[];           // [LT][dim + rot_dim] | partial sums [4][64][LT]
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * LT, h = blockIdx.y, qd = dim + rot_dim, od = kv_rank + rot_dim;
     const int nt = min(LT, T - t0);
+    float* red = qs + LT * qd;
     for (int e = threadIdx.x; e < LT * qd; e += 256) {
         const int tt = e / qd, i = e % qd;
         qs[e] = tt < nt ? q[((size_t)(t0 + tt) * heads + h) * qd + i] : 0.f;
     }
     __syncthreads();
     const WT* Wh = W_uk + (size_t)h * dim * kv_rank;
-    for (int r = threadIdx.x; r < kv_rank; r += 256) {
-        float acc[LT];
+    const int rl = threadIdx.x & 63, part = threadIdx.x >> 6, r = blockIdx.z * 64 + rl;
+    float acc[LT];
 #pragma unroll
-        for (int tt = 0; tt < LT; tt++) acc[tt] = 0.f;
-        for (int d = 0; d < dim; d++) {
+    for (int tt = 0; tt < LT; tt++) acc[tt] = 0.f;
+    if (r < kv_rank) {
+#pragma unroll 4
+        for (int d = part; d < dim; d += 4) {
             const float w = wld(Wh, (size_t)d * kv_rank + r);
 #pragma unroll
             for (int tt = 0; tt < LT; tt++) acc[tt] = fmaf(w, qs[tt * qd + d], acc[tt]);
         }
-#pragma unroll
-        for (int tt = 0; tt < LT; tt++) if (tt < nt) qa[((size_t)(t0 + tt) * heads + h) * od + r] = acc[tt];
     }
+#pragma unroll
+    for (int tt = 0; tt < LT; tt++) red[(part * 64 + rl) * LT + tt] = acc[tt];
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * LT; e += 256) {
+        const int rr = e / LT, tt = e % LT, ro = blockIdx.z * 64 + rr;
+        if (ro < kv_rank && tt < nt)
+            qa[((size_t)(t0 + tt) * heads + h) * od + ro] = (red[rr * LT + tt] + red[(64 + rr) * LT + tt]) + (red[(128 + rr) * LT + tt] + red[(192 + rr) * LT + tt]);
+    }
+    if (blockIdx.z != 0) return;
     const int base = pos_dev ? *pos_dev : p0;
     for (int e = threadIdx.x; e < nt * rot_dim; e += 256) {
         const int tt = e / rot_dim, i = e % rot_dim;
@@ -126,7 +141,8 @@ __global__ void __launch_bounds__(256) latent_q_absorb_kernel(float* __restrict_
     }
 }
 
-// grid (ceil(T / LT), heads).  ol [T, heads, kv_rank]; out [T, heads * vdim]; W_uv [heads * vdim, kv_rank].  A warp per output channel.
+// grid (ceil(T / LT), heads, ceil(vdim / 32)).  ol [T, heads, kv_rank]; out [T, heads * vdim]; W_uv [heads * vdim, kv_rank].  A warp per output
+// channel, 32 channels per CTA.
 template <typename WT>
 __global__ void __launch_bounds__(256) latent_v_up_kernel(float* __restrict__ out, const float* __restrict__ ol, const WT* __restrict__ W_uv, int T, int heads,
                                                           int vdim, int kv_rank) {
@@ -140,7 +156,7 @@ __global__ void __launch_bounds__(256) latent_v_up_kernel(float* __restrict__ ou
         os[e] = tt < nt ? ol[((size_t)(t0 + tt) * heads + h) * kv_rank + i] : 0.f;
     }
     __syncthreads();
-    for (int v = warp; v < vdim; v += 8) {
+    for (int v = blockIdx.z * 32 + warp; v < min(vdim, (int)blockIdx.z * 32 + 32); v += 8) {
         const WT* wr = W_uv + ((size_t)h * vdim + v) * kv_rank;
         float acc[LT];
 #pragma unroll
@@ -216,6 +232,171 @@ __global__ void __launch_bounds__(256) latent_unpad_kernel(float* __restrict__ o
     out[e] = o[e / vdim * vw + e % vdim];
 }
 
+// ---- attention of a few queries over ONE shared key / value head stored as rows (the absorbed form: every head scores the same rows) ----
+// A CTA takes a (query, key slice) and serves ALL heads from one copy of the rows in shared memory: tiles of 16 rows are loaded once
+// (16-byte copies) instead of once per head.  Warp w owns heads w, w + 8, ...: a tile's 16 scores of a head sit in 16 lanes x 2 halves
+// of the row (combined by one shuffle), the online softmax state of a head is uniform in its warp, the probabilities go through a
+// per-head line of shared memory that only the owning warp reads, and the weighted sum is lane-per-channel-pair with the four heads'
+// accumulators in registers.  Every CTA writes (max, sum, unnormalised vector) per head; latent_shared_merge_kernel joins the slices.
+constexpr int LS_KEYS = 16, LS_HB = 4, LS_CC = 8;      // rows per tile; heads per warp (heads <= 32); channel pairs per lane (vdim <= 512)
+
+template <typename KT> struct RowVec;
+template <> struct RowVec<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float (&v)[4]) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    __device__ static float2 pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
+};
+template <> struct RowVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const unsigned u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) { v[2 * e] = __uint_as_float(u[e] << 16); v[2 * e + 1] = __uint_as_float(u[e] & 0xFFFF0000u); }
+    }
+    __device__ static float2 pair(const __nv_bfloat16* p) { const unsigned u = *reinterpret_cast<const unsigned*>(p); return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u)); }
+};
+
+// grid (tokens, slices).  Q [tokens, heads, dim]; rows [*, row] with keys = the first dim numbers, values = the first vdim numbers.
+// part [tokens, slices, heads, vdim + 2].  dim, row multiples of RowVec::N; vdim even.
+template <typename KT>
+__global__ void __launch_bounds__(256) latent_shared_attn_kernel(float* __restrict__ part, const float* __restrict__ Q, const KT* __restrict__ rows,
+                                                                 const int* __restrict__ pos_dev, int p0, int heads, int dim, int vdim, int row, float scale) {
+    constexpr int VN = RowVec<KT>::N;
+    extern __shared__ __align__(16) unsigned char ls_raw[];
+    float* qs = reinterpret_cast<float*>(ls_raw);                              // [heads][dim]
+    float* ps = qs + (size_t)heads * dim;                                       // [heads][LS_KEYS]
+    KT* kt = reinterpret_cast<KT*>(ps + (size_t)heads * LS_KEYS);               // [LS_KEYS][dim + VN]: the pad keeps 16-byte reads of 8 rows on 8 bank groups
+    const int ldk = dim + VN;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, slice = blockIdx.y, n_slices = gridDim.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, key = lane & 15, half = lane >> 4;
+    const int n_keys = (pos_dev ? *pos_dev : p0) + t + 1;
+    const float* q = Q + (size_t)t * heads * dim;
+    for (int e = threadIdx.x * 4; e < heads * dim; e += 1024) *reinterpret_cast<float4*>(qs + e) = *reinterpret_cast<const float4*>(q + e);
+    float m[LS_HB], l[LS_HB], acc[LS_HB][LS_CC][2];
+#pragma unroll
+    for (int i = 0; i < LS_HB; i++) {
+        m[i] = -FLT_MAX; l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < LS_CC; c++) acc[i][c][0] = acc[i][c][1] = 0.f;
+    }
+    const int n_chunks = dim / VN;
+    for (int k0 = slice * LS_KEYS; k0 < n_keys; k0 += n_slices * LS_KEYS) {
+        __syncthreads();                                   // the previous tile is consumed (first pass: qs is written)
+        for (int e = threadIdx.x; e < LS_KEYS * n_chunks; e += 256) {
+            const int r = e / n_chunks, c = e - r * n_chunks;
+            const int src = min(k0 + r, n_keys - 1);       // rows past the last visible one are masked below
+            *reinterpret_cast<uint4*>(kt + (size_t)r * ldk + c * VN) = *reinterpret_cast<const uint4*>(rows + (size_t)src * row + c * VN);
+        }
+        __syncthreads();
+        const bool valid = k0 + key < n_keys;
+        // ---- scores: this lane's row, every second chunk of it, against the warp's heads ----
+        float sc[LS_HB] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = half; c < n_chunks; c += 2) {
+            float kv[VN];
+            RowVec<KT>::load(kt + (size_t)key * ldk + c * VN, kv);
+#pragma unroll
+            for (int i = 0; i < LS_HB; i++) {
+                const int h = warp + 8 * i;
+                if (h < heads) {
+                    const float* qh = qs + (size_t)h * dim + c * VN;
+#pragma unroll
+                    for (int e = 0; e < VN; e += 4) {
+                        const float4 qv = *reinterpret_cast<const float4*>(qh + e);
+                        sc[i] = fmaf(qv.x, kv[e], sc[i]); sc[i] = fmaf(qv.y, kv[e + 1], sc[i]); sc[i] = fmaf(qv.z, kv[e + 2], sc[i]); sc[i] = fmaf(qv.w, kv[e + 3], sc[i]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < LS_HB; i++) {
+            const int h = warp + 8 * i;
+            if (h >= heads) continue;                      // uniform in the warp
+            float s = sc[i] + __shfl_xor_sync(0xFFFFFFFFu, sc[i], 16);
+            s = valid ? s * scale : -FLT_MAX;
+            float mt = s;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xFFFFFFFFu, mt, o));
+            const float mn = fmaxf(m[i], mt);
+            const float corr = expf(m[i] - mn), pk = valid ? expf(s - mn) : 0.f;
+            float sum = pk;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+            l[i] = l[i] * corr + sum;
+            m[i] = mn;
+            if (half == 0) ps[h * LS_KEYS + key] = pk;
+#pragma unroll
+            for (int c = 0; c < LS_CC; c++) { acc[i][c][0] *= corr; acc[i][c][1] *= corr; }
+        }
+        __syncwarp();                                       // a head's probabilities are read by its own warp only
+        // ---- weighted sum: lane owns channel pairs 2 lane + 64 c ----
+#pragma unroll 4
+        for (int k = 0; k < LS_KEYS; k++) {
+            float pk[LS_HB];
+#pragma unroll
+            for (int i = 0; i < LS_HB; i++) pk[i] = warp + 8 * i < heads ? ps[(warp + 8 * i) * LS_KEYS + k] : 0.f;
+#pragma unroll
+            for (int c = 0; c < LS_CC; c++) {
+                const int ch = 2 * lane + 64 * c;
+                if (ch < vdim) {
+                    const float2 v = RowVec<KT>::pair(kt + (size_t)k * ldk + ch);
+#pragma unroll
+                    for (int i = 0; i < LS_HB; i++) { acc[i][c][0] = fmaf(pk[i], v.x, acc[i][c][0]); acc[i][c][1] = fmaf(pk[i], v.y, acc[i][c][1]); }
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < LS_HB; i++) {
+        const int h = warp + 8 * i;
+        if (h >= heads) continue;
+        float* dst = part + (((size_t)t * n_slices + slice) * heads + h) * (vdim + 2);
+        if (lane == 0) { dst[0] = m[i]; dst[1] = l[i]; }
+#pragma unroll
+        for (int c = 0; c < LS_CC; c++) {
+            const int ch = 2 * lane + 64 * c;
+            if (ch < vdim) { dst[2 + ch] = acc[i][c][0]; dst[3 + ch] = acc[i][c][1]; }
+        }
+    }
+}
+
+// grid (tokens, heads, ceil(vdim / 64)): out [t, h, :] = sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M).  Thread (channel, g) sums
+// every fourth slice of its channel; the four partial sums meet in shared memory.
+__global__ void __launch_bounds__(256) latent_shared_merge_kernel(float* __restrict__ out, const float* __restrict__ part, int n_slices, int heads, int vdim) {
+    extern __shared__ __align__(16) float wsm[];           // [n_slices]
+    __shared__ float red[8];
+    __shared__ float sums[4][64];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* base = part + ((size_t)t * n_slices * heads + h) * (vdim + 2);
+    const size_t step = (size_t)heads * (vdim + 2);
+    float mx = -FLT_MAX;
+    for (int s = threadIdx.x; s < n_slices; s += 256) mx = fmaxf(mx, base[s * step]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    float M = -FLT_MAX;
+#pragma unroll
+    for (int w = 0; w < 8; w++) M = fmaxf(M, red[w]);
+    float ls = 0.f;
+    for (int s = threadIdx.x; s < n_slices; s += 256) { const float w = expf(base[s * step] - M); wsm[s] = w; ls = fmaf(base[s * step + 1], w, ls); }
+    const float L = block_sum_256(ls, red);                // its barriers also publish wsm
+    const int cl = threadIdx.x & 63, g = threadIdx.x >> 6, c = blockIdx.z * 64 + cl;
+    float v = 0.f;
+    if (c < vdim) {
+#pragma unroll 8
+        for (int s = g; s < n_slices; s += 4) v = fmaf(base[s * step + 2 + c], wsm[s], v);
+    }
+    sums[g][cl] = v;
+    __syncthreads();
+    if (g == 0 && c < vdim) out[((size_t)t * heads + h) * vdim + c] = ((sums[0][cl] + sums[1][cl]) + (sums[2][cl] + sums[3][cl])) / L;
+}
+
 }  // namespace
 
 void latent_prep(float* cq, int q_rank, const float* q_gain, const float* dkv, int kv_rank, int rot_dim, const float* kv_gain, float eps, void* cache,
@@ -235,10 +416,10 @@ void latent_prep(float* cq, int q_rank, const float* q_gain, const float* dkv, i
 void latent_q_absorb(float* qa, const float* q, const void* W_uk, DType dt, int T, int heads, int dim, int rot_dim, int kv_rank, int rot_dims,
                      bool interleaved, float rot_base, const int* pos_dev, int p0, cudaStream_t s) {
     if (T <= 0) return;
-    const size_t smem = sizeof(float) * LT * (size_t)(dim + rot_dim);
-    NT_CHECK(smem <= 48 * 1024, "latent_q_absorb: query heads wider than 1536 are not covered");
+    const size_t smem = sizeof(float) * (LT * (size_t)(dim + rot_dim) + 4 * 64 * LT);
+    NT_CHECK(smem <= 48 * 1024, "latent_q_absorb: query heads wider than 1280 are not covered");
     const double l2b = std::log2((double)rot_base);
-    const dim3 grid((T + LT - 1) / LT, heads);
+    const dim3 grid((T + LT - 1) / LT, heads, (kv_rank + 63) / 64);
 #define NT_QA(TY) launch_k(latent_q_absorb_kernel<TY>, grid, dim3(256), smem, s, qa, q, static_cast<const TY*>(W_uk), T, heads, dim, rot_dim, kv_rank, rot_dims, \
                            interleaved ? 1 : 0, l2b, pos_dev, p0)
     if (dt == DType::F32) NT_QA(float); else if (dt == DType::F16) NT_QA(__half); else if (dt == DType::BF16) NT_QA(__nv_bfloat16);
@@ -251,7 +432,7 @@ void latent_v_up(float* out, const float* ol, const void* W_uv, DType dt, int T,
     if (T <= 0) return;
     const size_t smem = sizeof(float) * LT * (size_t)kv_rank;
     NT_CHECK(smem <= 48 * 1024, "latent_v_up: latents wider than 1536 are not covered");
-    const dim3 grid((T + LT - 1) / LT, heads);
+    const dim3 grid((T + LT - 1) / LT, heads, (vdim + 31) / 32);
 #define NT_VU(TY) launch_k(latent_v_up_kernel<TY>, grid, dim3(256), smem, s, out, ol, static_cast<const TY*>(W_uv), T, heads, vdim, kv_rank)
     if (dt == DType::F32) NT_VU(float); else if (dt == DType::F16) NT_VU(__half); else if (dt == DType::BF16) NT_VU(__nv_bfloat16);
     else NT_CHECK(false, "latent_v_up: dense dtypes only");
@@ -289,6 +470,50 @@ void latent_unpad(float* out, const float* o, int T, int heads, int vdim, int vw
     if (!total) return;
     launch_k(latent_unpad_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, out, o, vdim, vw, total);
     count_launch();
+}
+
+// ---- attention over one shared key / value head (see latent_shared_attn_kernel) ----
+namespace { constexpr int LS_MAX_PARTS = 512; }           // (query, slice) pairs per launch: bounds the scratch
+
+bool attention_shared_rows_supported(int heads, int dim, int vdim, int row, DType cache_dt, const void* cache) {
+    static const bool off = getenv("NT_B200_NO_SHARED_ROWS") != nullptr;
+    if (off || (cache_dt != DType::F32 && cache_dt != DType::BF16)) return false;
+    const int vn = cache_dt == DType::F32 ? 4 : 8;
+    const size_t smem = sizeof(float) * ((size_t)heads * dim + (size_t)heads * LS_KEYS) + (size_t)LS_KEYS * (dim + vn) * (cache_dt == DType::F32 ? 4 : 2);
+    return heads >= 1 && heads <= 8 * LS_HB && dim % vn == 0 && row % vn == 0 && dim <= row && vdim <= row && vdim % 2 == 0 && vdim <= 64 * LS_CC &&
+           (reinterpret_cast<uintptr_t>(cache) & 15) == 0 && smem <= 200 * 1024;
+}
+int attention_shared_rows_slices(int tokens, int max_seq) {
+    return std::max(1, std::min({(max_seq + LS_KEYS - 1) / LS_KEYS, LS_MAX_PARTS / std::max(1, tokens), 128}));      // one query: up to 128 CTAs
+}
+size_t attention_shared_rows_scratch_floats(int heads, int vdim) { return (size_t)LS_MAX_PARTS * heads * ((size_t)vdim + 2); }
+
+// out [tokens, heads, vdim]; Q [tokens, heads, dim]; scratch >= attention_shared_rows_scratch_floats.  The grid depends on tokens and
+// max_seq only, never on the position: the captured decode step replays it unchanged.
+void attention_shared_rows(float* out, const float* Q, const void* cache, DType cache_dt, int tokens, const int* pos_dev, int p0, int max_seq, int heads, int dim,
+                           int vdim, int row, float scale, float* scratch, cudaStream_t s) {
+    if (tokens <= 0) return;
+    NT_CHECK(attention_shared_rows_supported(heads, dim, vdim, row, cache_dt, cache), "attention_shared_rows: shape not covered");
+    const bool f32 = cache_dt == DType::F32;
+    const int vn = f32 ? 4 : 8;
+    const size_t smem = sizeof(float) * ((size_t)heads * dim + (size_t)heads * LS_KEYS) + (size_t)LS_KEYS * (dim + vn) * (f32 ? 4 : 2);
+    for (int t0 = 0; t0 < tokens; t0 += LS_MAX_PARTS) {           // long portions (exact mode): blocks of queries with one slice each
+        const int nt = std::min(LS_MAX_PARTS, tokens - t0);
+        const int slices = attention_shared_rows_slices(nt, max_seq);
+        static unsigned long long cfg_f = 0, cfg_b = 0;
+        if (f32) {
+            opt_in_dynamic_smem(latent_shared_attn_kernel<float>, 200 * 1024, cfg_f);
+            launch_k(latent_shared_attn_kernel<float>, dim3(nt, slices), dim3(256), smem, s, scratch, Q + (size_t)t0 * heads * dim, static_cast<const float*>(cache), pos_dev,
+                     p0 + t0, heads, dim, vdim, row, scale);
+        } else {
+            opt_in_dynamic_smem(latent_shared_attn_kernel<__nv_bfloat16>, 200 * 1024, cfg_b);
+            launch_k(latent_shared_attn_kernel<__nv_bfloat16>, dim3(nt, slices), dim3(256), smem, s, scratch, Q + (size_t)t0 * heads * dim,
+                     static_cast<const __nv_bfloat16*>(cache), pos_dev, p0 + t0, heads, dim, vdim, row, scale);
+        }
+        count_launch();
+        launch_k(latent_shared_merge_kernel, dim3(nt, heads, (vdim + 63) / 64), dim3(256), sizeof(float) * slices, s, out + (size_t)t0 * heads * vdim, (const float*)scratch, slices, heads, vdim);
+        count_launch();
+    }
 }
 
 }}  // namespace nt::b200

@@ -270,6 +270,19 @@ void nt_b200_attention_rows(float* out, const float* Q, const void* cache, int c
     a.heads = heads; a.kv_heads = 1; a.dim = dim; a.vdim = vdim; a.scale = scale; a.k_stride = row; a.v_stride = row;
     attention_window(out, Q, cache, cache, (nt::DType)cache_dtype, tokens, nullptr, p0, max_seq, a, static_cast<cudaStream_t>(stream));
 }
+// The same attention with every head served from one shared-memory copy of the rows (key slices merged by a second launch).
+// -1: shape not covered.  Scratch is allocated and freed here.
+int nt_b200_attention_rows_shared(float* out, const float* Q, const void* cache, int cache_dtype, int tokens, int p0, int heads, int dim, int vdim, int row, float scale,
+                                  int max_seq, void* stream) {
+    if (!attention_shared_rows_supported(heads, dim, vdim, row, (nt::DType)cache_dtype, cache)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* scratch = nullptr;
+    NT_CUDA_CHECK(cudaMalloc(&scratch, sizeof(float) * attention_shared_rows_scratch_floats(heads, vdim)));
+    attention_shared_rows(out, Q, cache, (nt::DType)cache_dtype, tokens, nullptr, p0, max_seq, heads, dim, vdim, row, scale, scratch, s);
+    NT_CUDA_CHECK(cudaStreamSynchronize(s));
+    cudaFree(scratch);
+    return 0;
+}
 void nt_b200_ssm_conv(float* out, const float* u, int ld, int col0, float* conv_state, const float* w, const float* b, int tokens, int ch, int taps, int p0, void* stream) {
     ssm_conv(out, u, ld, col0, conv_state, w, b, tokens, ch, taps, nullptr, p0, static_cast<cudaStream_t>(stream));
 }

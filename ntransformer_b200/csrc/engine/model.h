@@ -181,6 +181,7 @@ private:
         void *k = nullptr, *v = nullptr, *ws = nullptr;
         float *q = nullptr, *o = nullptr, *c32 = nullptr, *ku = nullptr, *vu = nullptr;
     } lat_;
+    float* lat_part_ = nullptr;           // absorbed latent attention: (max, sum, vector) per (query, key slice, head), joined by a merge launch
     bool latent_expand_ok(const LayerSpec& S, int T) const;
     void ensure_latent_scratch(const LayerSpec& S, size_t rows, size_t tokens);
     void latent_attention_rows(int i, int T, int p0, const float* q, float* out, cudaStream_t s);   // out [T, heads * vdim]

@@ -297,6 +297,10 @@ bool Model::finalize_spec() {
         dec_.y = dmalloc<float>(m1);
         for (float*& t : dec_.t) t = dmalloc<float>(m1);
         moe_sel_ = dmalloc<int>(topmax); moe_wt_ = dmalloc<float>(topmax); moe_act_ = dmalloc<float>(moe_act);
+        size_t parts = 0;                          // per-slice partial results of the attention that serves all heads from one copy of the rows
+        for (const LayerSpec& S : cfg_.layers)
+            if (S.mixer == MixerKind::ATTN_LATENT) parts = std::max(parts, attention_shared_rows_scratch_floats(S.heads, S.latent.kv_rank));
+        if (parts) { lat_part_ = dmalloc<float>(parts); owned_.push_back(lat_part_); }
     }
     hidden_ = dmalloc<float>(hidden);
     xnorm_ = dmalloc<float>(hidden);
@@ -822,7 +826,10 @@ void Model::layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev,
         latent_q_absorb(qa, q, L.w_uk.ptr, L.w_uk.dtype, T, S.heads, S.dim, A.rot_dim, A.kv_rank, S.rot.dims, S.rot.interleaved, S.rot.base, pos_dev, p0, s);
         WindowAttn a;                       // one key / value head: keys are the whole cache rows, values their first kv_rank numbers
         a.heads = S.heads; a.kv_heads = 1; a.dim = row; a.vdim = A.kv_rank; a.scale = S.scale; a.k_stride = row; a.v_stride = row;
-        attention_window(ol, qa, kcs_[(size_t)i], kcs_[(size_t)i], cache_dt_, T, pos_dev, p0, cfg_.max_seq_len, a, s);
+        if (lat_part_ && attention_shared_rows_supported(S.heads, row, A.kv_rank, row, cache_dt_, kcs_[(size_t)i]))
+            attention_shared_rows(ol, qa, kcs_[(size_t)i], cache_dt_, T, pos_dev, p0, cfg_.max_seq_len, S.heads, row, A.kv_rank, row, S.scale, lat_part_, s);
+        else
+            attention_window(ol, qa, kcs_[(size_t)i], kcs_[(size_t)i], cache_dt_, T, pos_dev, p0, cfg_.max_seq_len, a, s);
         latent_v_up(o, ol, L.w_uv.ptr, L.w_uv.dtype, T, S.heads, S.vdim, A.kv_rank, s);
         rows_matmul(B.y, o, L.wo, T, s);
         }

@@ -256,6 +256,12 @@ void latent_expand_pack(void* kfull, void* vfull, const float* ku, const float* 
 void latent_q_rot_pad(float* qp, const float* q, int T, int heads, int dim, int rot_dim, int kw, int rot_dims, bool interleaved, float rot_base, int p0,
                       cudaStream_t s);
 void latent_unpad(float* out, const float* o, int T, int heads, int vdim, int vw, cudaStream_t s);
+// Attention of a few queries over ONE key / value head stored as rows (keys: the first dim numbers of a row, values: the first vdim),
+// every head served from one shared-memory copy of the rows; key slices merged by a second launch.  Full causal mask.
+bool attention_shared_rows_supported(int heads, int dim, int vdim, int row, DType cache_dt, const void* cache);
+size_t attention_shared_rows_scratch_floats(int heads, int vdim);
+void attention_shared_rows(float* out, const float* Q, const void* cache, DType cache_dt, int tokens, const int* pos_dev, int p0, int max_seq, int heads, int dim,
+                           int vdim, int row, float scale, float* scratch, cudaStream_t s);
 // attention_prefill_mma.cu: full causal attention of `tokens` queries [tokens, heads, kw] at positions p0.. over BF16 per-head keys
 // [rows, heads, kw] and values [rows, heads, vw]; (kw, vw) from attention_heads_mma_widths.  out [tokens, heads, vw].
 bool attention_heads_mma_widths(int key_dim, int value_dim, int* kw, int* vw);
