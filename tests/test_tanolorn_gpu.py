@@ -117,7 +117,7 @@ def test_latent_attention_in_the_latent_space(cache, H, D, R, V, kv_rank, dims):
 @pytest.mark.parametrize("H,D,R,V,kv_rank,dims", [(3, 8, 6, 10, 18, 6), (32, 16, 8, 8, 64, 8), (5, 4, 4, 3, 12, 2), (2, 24, 16, 40, 304, 12), (9, 6, 0, 5, 16, 0), (1, 8, 8, 8, 8, 8)])
 def test_all_heads_from_one_copy_of_the_rows(cache, H, D, R, V, kv_rank, dims):
     """The form that loads each tile of rows once for all heads and merges key slices in a second launch: prompts, portions, decoded
-    tokens, more heads than warps, a contexts that ends inside a 16-row tile, more tiles than slices."""
+    tokens, more heads than warps, a context that ends inside a 16-row tile, more tiles than slices."""
     rng = np.random.default_rng(H * 10 + D)
     n, base, scale = 700, 50.0, (D + R) ** -0.5
     tdt = torch.float32 if cache == DType.F32 else torch.bfloat16
