@@ -60,7 +60,8 @@ template <int HD, int HDV, bool BF>
 __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__ out, const float* __restrict__ Q,
                                                              const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                              int seq_len, int start_pos, int n_heads, int n_kv, int max_seq,
-                                                             float scale, int window, int keep, float softcap, int maps, int chunk) {
+                                                             float scale, int window, int keep, float softcap, int maps, int chunk,
+                                                             const float* __restrict__ sink, int joint_v) {
     constexpr int LD = HD + PAD, LDV = HDV + PAD, KS = HD / 16, NT = HDV / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sK = reinterpret_cast<__half*>(smem_raw);                 // [2][BKV][LD]
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
         for (int c = threadIdx.x; c < BKV * CHV; c += 128) {
             const int row = c / CHV, ch = c % CHV;
             const int key = min(tile_of(j) * BKV + row, max_seq - 1);
-            cp_async16(sV + ((size_t)st * BKV + row) * LDV + ch * 8, vc + ((size_t)key * n_kv + vh) * HDV + ch * 8);
+            cp_async16(sV + ((size_t)st * BKV + row) * LDV + ch * 8, vc + (joint_v ? (size_t)key : (size_t)key * n_kv + vh) * HDV + ch * 8);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -199,6 +200,14 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
     }
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    if (sink) {                     // exp(sink) joins the denominator; the maximum is raised to the sink first so nothing overflows
+        const float sk = sink[head / maps];
+        const float n0 = fmaxf(m0, sk), n1 = fmaxf(m1, sk);
+        const float f0 = __expf(m0 - n0), f1 = __expf(m1 - n1);
+        l0 = l0 * f0 + __expf(sk - n0); l1 = l1 * f1 + __expf(sk - n1);
+#pragma unroll
+        for (int n = 0; n < NT; n++) { o[n][0] *= f0; o[n][1] *= f0; o[n][2] *= f1; o[n][3] *= f1; }
+    }
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
 #pragma unroll
     for (int n = 0; n < NT; n++) {
@@ -210,12 +219,13 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
 
 template <int HD, int HDV, bool BF>
 void launch(float* out, const float* Q, const __half* kc, const __half* vc, int seq_len, int start_pos, int n_heads, int n_kv,
-            int max_seq, float scale, int window, int keep, float softcap, cudaStream_t s, int maps = 1, int chunk = 0) {
+            int max_seq, float scale, int window, int keep, float softcap, cudaStream_t s, int maps = 1, int chunk = 0, const float* sink = nullptr,
+            int joint_v = 0) {
     const int smem = 2 * BKV * (HD + PAD + HDV + PAD) * (int)sizeof(__half);
     static unsigned long long configured = 0;      // bit per device id
     opt_in_dynamic_smem(prefill_mma_kernel<HD, HDV, BF>, (int)(smem), configured);
     prefill_mma_kernel<HD, HDV, BF><<<dim3((seq_len + BQ - 1) / BQ, n_heads * maps), 128, smem, s>>>(out, Q, kc, vc, seq_len, start_pos, n_heads * maps, n_kv,
-                                                                                                    max_seq, scale, window, keep, softcap, maps, chunk);
+                                                                                                    max_seq, scale, window, keep, softcap, maps, chunk, sink, joint_v);
     NT_LAUNCH_CHECK();
     count_launch();
 }
@@ -238,13 +248,15 @@ void attention_prefill_mma(float* out, const float* Q, const void* kc, const voi
 // two score maps per head, at least 16 queries.
 bool attention_window_mma_supported(int tokens, const WindowAttn& a, DType cache_dt) {
     const bool shape = (a.dim == a.vdim && (a.dim == 64 || a.dim == 128)) || (a.vdim == 2 * a.dim && (a.dim == 32 || a.dim == 64));
-    return cache_dt == DType::BF16 && shape && a.k_stride == 0 && a.v_stride == 0 && a.maps >= 1 && a.maps <= 2 && tokens >= 16 && a.kv_heads > 0 && a.heads % a.kv_heads == 0;
+    // joint values: one value row of width vdim per key, packed (the stride equals the width)
+    const bool strides = a.k_stride == 0 && (a.joint_v ? (a.v_stride == a.vdim && a.maps == 1) : a.v_stride == 0);
+    return cache_dt == DType::BF16 && shape && strides && a.maps >= 1 && a.maps <= 2 && tokens >= 16 && a.kv_heads > 0 && a.heads % a.kv_heads == 0;
 }
 void attention_window_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int max_seq, const WindowAttn& a,
                           cudaStream_t s) {
     const __half* k = static_cast<const __half*>(kc);       // 16-bit words either way; the BF instantiation reads them as BF16
     const __half* v = static_cast<const __half*>(vc);
-#define NT_AW(D, V) launch<D, V, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s, a.maps, a.chunk)
+#define NT_AW(D, V) launch<D, V, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s, a.maps, a.chunk, a.sink, a.joint_v)
     if (a.dim == 128) NT_AW(128, 128);
     else if (a.dim == 64 && a.vdim == 64) NT_AW(64, 64);
     else if (a.dim == 64) NT_AW(64, 128);

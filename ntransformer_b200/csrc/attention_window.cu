@@ -10,6 +10,8 @@
 //   with a running (max, sum, acc) each, merged through shared memory at the end; for a single decoded token the keys of a head
 //   are further split over the CTAs of a thread-block cluster and merged through the leader's distributed shared memory.  Prompts over a BF16 cache with equal key and
 //   value width go to the tiled tensor-core form in attention_prefill_mma.cu instead.
+// WindowAttn::sink adds exp(sink_h) to head h's denominator (a learned term without key or value); WindowAttn::joint_v makes every query
+// head sum one value row per key that spans all value heads, which attention_heads.cu's talk_mix turns into head-mixed softmax weights.
 // Compiled WITHOUT --use_fast_math (tanhf / expf at full precision).
 #include "kernels_internal.h"
 #include "ring.cuh"
@@ -126,7 +128,7 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
         for (int kk = 0; kk < 32; kk++) {
             const float pk = __shfl_sync(0xFFFFFFFFu, p, kk);
             const int jk = __shfl_sync(0xFFFFFFFFu, j, kk);
-            const KT* vr = vc + (size_t)jk * vstride + (size_t)g * a.vdim;
+            const KT* vr = vc + (size_t)jk * vstride + (a.joint_v ? 0 : (size_t)g * a.vdim);
 #pragma unroll
             for (int e = 0; e < AW_MAXV; e++) {
                 const int i = lane + 32 * e;
@@ -146,10 +148,13 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     for (int w = 0; w < AW_WARPS; w++) L += ls[w] * expf(ms[w] - M);
     float* o = out + (size_t)t * a.heads * a.maps * a.vdim + (size_t)hm * a.vdim;
     if (splits == 1) {
+        // the sink joins the denominator as one more term exp(sink - max): the maximum is raised to it first so nothing overflows
+        float fix = 1.f;
+        if (a.sink) { const float sk = a.sink[h], M2 = fmaxf(M, sk); fix = expf(M - M2); L = L * fix + expf(sk - M2); }
         for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
             float v = 0.f;
             for (int w = 0; w < AW_WARPS; w++) v += accs[w * a.vdim + i] * expf(ms[w] - M);
-            o[i] = v / L;
+            o[i] = v * fix / L;
         }
         return;
     }
@@ -166,7 +171,8 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     if (rank != 0) return;
     float MM = -FLT_MAX;
     for (int r = 0; r < splits; r++) MM = fmaxf(MM, part[(size_t)r * (a.vdim + 2)]);
-    float LL = 0.f;
+    if (a.sink) MM = fmaxf(MM, a.sink[h]);
+    float LL = a.sink ? expf(a.sink[h] - MM) : 0.f;
     for (int r = 0; r < splits; r++) LL += part[(size_t)r * (a.vdim + 2) + 1] * expf(part[(size_t)r * (a.vdim + 2)] - MM);
     for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
         float v = 0.f;
@@ -233,6 +239,7 @@ void attention_window(float* out, const float* Q, const void* kc, const void* vc
     const size_t smem = sizeof(float) * ((size_t)((a.dim + 3) & ~3) + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS + (size_t)splits * (a.vdim + 2));
     cudaLaunchConfig_t cfg{};
     NT_CHECK(a.maps >= 1, "attention_window: maps >= 1");
+    NT_CHECK(!a.joint_v || (a.v_stride > 0 && a.maps == 1), "attention_window: joint values need the value row stride and one map");
     cfg.gridDim = dim3(tokens, a.heads * a.maps, splits); cfg.blockDim = dim3(AW_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

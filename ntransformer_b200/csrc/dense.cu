@@ -73,10 +73,10 @@ __device__ __forceinline__ void streams_update(const StreamsIO& sio, int N, int 
 }
 
 struct DenseMats {
-    const unsigned char* W[3];
-    float* y[3];
-    int out[3];
-    size_t pitch[3];
+    const unsigned char* W[DENSE_MAX_MATS];
+    float* y[DENSE_MAX_MATS];
+    int out[DENSE_MAX_MATS];
+    size_t pitch[DENSE_MAX_MATS];
     int n;
 };
 
@@ -150,17 +150,18 @@ __global__ void __launch_bounds__(DV_WARPS * 32) gemv_dense_kernel(DenseMats m, 
         for (int i = threadIdx.x; i < K; i += DV_WARPS * 32) xs[i] = xs[i] * inv * norm_w[i];
     }
     __syncthreads();
-    const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU;
-    const int total = glu ? m.out[0] : m.out[0] + (m.n > 1 ? m.out[1] : 0) + (m.n > 2 ? m.out[2] : 0);
+    const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU || ep == DENSE_REGLU;
+    int total = m.out[0];
+    if (!glu) for (int i = 1; i < m.n; i++) total += m.out[i];
     for (int r = blockIdx.x * DV_WARPS + warp; r < total; r += gridDim.x * DV_WARPS) {
         if (glu) {
             const float g = dense_row_dot<T>(m.W[0] + (size_t)r * m.pitch[0], xs, K, lane, vec);
             const float u = dense_row_dot<T>(m.W[1] + (size_t)r * m.pitch[1], xs, K, lane, vec);
-            if (lane == 0) m.y[0][r] = (ep == DENSE_GEGLU ? gelu_tanh_f(g) : silu_f(g)) * u;
+            if (lane == 0) m.y[0][r] = (ep == DENSE_GEGLU ? gelu_tanh_f(g) : ep == DENSE_REGLU ? fmaxf(g, 0.f) : silu_f(g)) * u;
             continue;
         }
         int mi = 0, row = r;
-        if (row >= m.out[0]) { row -= m.out[0]; mi = 1; if (row >= m.out[1]) { row -= m.out[1]; mi = 2; } }
+        while (mi + 1 < m.n && row >= m.out[mi]) { row -= m.out[mi]; mi++; }
         const float v = dense_row_dot<T>(m.W[mi] + (size_t)row * m.pitch[mi], xs, K, lane, vec);
         if (lane == 0 && ep == DENSE_STREAMS) streams_update(sio, m.out[0], row, v);
         else if (lane == 0) {
@@ -218,9 +219,9 @@ __global__ void __launch_bounds__(256) gemm_dense_kernel(float* __restrict__ C, 
     }
 }
 
-__global__ void glu_mul_kernel(float* __restrict__ out, const float* __restrict__ gate, const float* __restrict__ up, size_t n, int gelu) {
+__global__ void glu_mul_kernel(float* __restrict__ out, const float* __restrict__ gate, const float* __restrict__ up, size_t n, int act) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = (gelu ? gelu_tanh_f(gate[i]) : silu_f(gate[i])) * up[i];
+    if (i < n) out[i] = (act == 1 ? gelu_tanh_f(gate[i]) : act == 2 ? fmaxf(gate[i], 0.f) : silu_f(gate[i])) * up[i];
 }
 __global__ void scaled_add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ row_scale, float alpha,
                                        size_t n, int cols) {
@@ -239,11 +240,11 @@ bool dense_dtype(DType dt) { return dt == DType::F32 || dt == DType::F16 || dt =
 
 void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s,
                 const float* norm_w, float eps, const StreamsIO* sio_p) {
-    NT_CHECK(n_mat >= 1 && n_mat <= 3, "gemv_dense: 1..3 matrices");
+    NT_CHECK(n_mat >= 1 && n_mat <= DENSE_MAX_MATS, "gemv_dense: too many matrices for one launch");
     const StreamsIO sio = sio_p ? *sio_p : StreamsIO();
     NT_CHECK(ep != DENSE_STREAMS || (n_mat == 1 && sio.X_out && sio.M && sio.b && sio.S >= 1 && sio.S <= 16), "gemv_dense: the streams epilogue takes one matrix and the stream tables");
     NT_CHECK(!sio.X_in || (sio.S >= 1 && sio.S <= 16), "gemv_dense: 1..16 streams");
-    const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU;
+    const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU || ep == DENSE_REGLU;
     NT_CHECK(!glu || (n_mat == 2 && mats[0].out == mats[1].out), "gemv_dense: a gated epilogue takes two matrices of equal height");
     const DType dt = mats[0].dtype;
     NT_CHECK(dense_dtype(dt), "gemv_dense: dense dtypes only");
@@ -287,9 +288,9 @@ void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pi
     count_launch();
 }
 
-void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s) {
+void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s, bool relu) {
     if (!n) return;
-    glu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out, gate, up, n, gelu ? 1 : 0);
+    glu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out, gate, up, n, relu ? 2 : (gelu ? 1 : 0));
     NT_LAUNCH_CHECK();
     count_launch();
 }

@@ -31,6 +31,7 @@ struct ModelConfig {                       // reference src/model/config.h:16-58
     float norm_gain_offset = 0.0f;         // block / final norm gains are stored minus this (1: "zero-centred" gains); added once when the model is finalized
     int side_dim = 0;                      // > 0: after every layer the token's own slice [layer * side_dim, +side_dim) of a second embedding table,
                                            // gated by gelu(W_g x), projected back and RMS-normed, is added to the residual (POST_NORM form)
+    float skip_scale = 1.0f;               // a of the SUM_NORM block form
     bool layer_spec() const { return !layers.empty(); }
     void print() const;
 };

@@ -11,15 +11,22 @@ enum class MixerKind { ATTN_ROPE_CAUSAL = 0,     // rotary positions, full causa
                        ATTN_WINDOW = 1,          // no positions in the scores; sliding window + kept first tokens; soft-capped scores
                        ATTN_LATENT = 2,          // queries and keys / values through low-rank latents; the cache holds the normed key / value latent
                                                  // and one rotated key part shared by all heads; scored in the latent space (LatentSpec)
-                       SSM_SCAN = 3 };           // selective state-space recurrence with a short causal convolution in front (ScanSpec); no cache rows,
+                       SSM_SCAN = 3,             // selective state-space recurrence with a short causal convolution in front (ScanSpec); no cache rows,
                                                  // a fixed-size state per sequence instead
-enum class QKNorm { NONE = 0, WHOLE = 1 };       // WHOLE: one RMS norm across ALL heads of the projection (gain vector of that length)
-enum class GluAct { SILU = 0, GELU_TANH = 1 };
+                       DELTA_RULE = 4,           // gated delta-rule recurrence (DeltaSpec): a matrix state per head that is decayed per key channel,
+                                                 // corrected towards the new value along the new key and read with the query; no cache rows
+                       BRANCHES = 5 };           // several mixers side by side reading the same input; their outputs are summed with fixed weights
+                                                 // (LayerSpec::branches / branch_scale); each branch keeps its own cache rows or state
+enum class QKNorm { NONE = 0, WHOLE = 1,         // WHOLE: one RMS norm across ALL heads of the projection (gain vector of that length)
+                    PER_HEAD = 2 };              // every head is RMS-normed on its own with one gain vector of the head's width shared by all heads
+enum class GluAct { SILU = 0, GELU_TANH = 1, RELU = 2 };
 enum class BlockForm { SEQUENTIAL = 0,           // x += mixer(norm1 x) ; x += ff(norm2 x)
                        PARALLEL = 1,             // h = norm1 x ; x += m * (ls1 * mixer(h) + ls2 * ff(h))
                        STREAMS = 2,              // SEQUENTIAL over several residual streams: a sublayer reads a learned blend of the streams and
                                                  // its output enters every stream through a learned stream-mixing matrix (ModelConfig::streams)
-                       POST_NORM = 3 };          // x += norm1(mixer(x)) ; x += norm2(ff(x)): the sublayers read x itself, the norm sits on their output
+                       POST_NORM = 3,            // x += norm1(mixer(x)) ; x += norm2(ff(x)): the sublayers read x itself, the norm sits on their output
+                       SUM_NORM = 4 };           // x <- norm1(a x + mixer(x)) ; x <- norm2(a x + ff(x)): the norm sits on the residual sum itself, the
+                                                 // skip path is multiplied by a = ModelConfig::skip_scale
 enum class FfKind { GLU = 0,                     // W_down (act(W_gate h) * W_up h)
                     MOE_RELU2 = 1,               // routed experts W_down relu(W_up h)^2, top-k softmax over the chosen logits, optional gated shared expert
                     MOE_GLU = 2 };               // routed gated experts W_down (act(W_gate h) * W_up h); how they are chosen and weighted: RouteSpec
@@ -34,6 +41,7 @@ struct RotarySpec {
     float base = 10000.f;
     bool interleaved = true;     // pairs (2i, 2i+1); false: (i, i + dims/2)
     float factor = 0.f, original = 0.f, fast = 0.f, slow = 0.f;
+    float divide = 1.f;          // linear position scaling: every angular frequency is divided by this
 };
 
 // Low-rank attention.  q = W_uq rms(W_dq h): per head [dim unrotated | rot_dim rotated].  W_dkv h = [kv_rank | rot_dim]: the first part,
@@ -55,6 +63,16 @@ struct ScanSpec {
 struct RouteSpec {
     bool sigmoid = false, correction = false;
     int groups = 0, keep = 0;
+};
+
+// Gated delta rule.  q, k [kv_heads, dim] and v [heads, vdim] come from projections followed by a short causal convolution
+// (LayerSpec::conv taps) and SiLU; q and k are scaled to unit length per head (q also by dim^-1/2).  Per value head h (reading q / k head
+// h / (heads / kv_heads)) with state S [dim, vdim] in F32:  S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, where
+// beta = sigmoid(W_b x) per head and g = exp(-exp(A_log_h) softplus(W_a2 W_a1 x + dt_bias)) per head and key channel (decay_rank = rows of
+// W_a1).  o is RMS-normed per head (gain shared by the heads) and multiplied by sigmoid(W_g2 W_g1 x) (gate_rank = rows of W_g1).
+// The sequence's state is S plus the last taps - 1 inputs of the three convolutions.
+struct DeltaSpec {
+    int decay_rank = 0, gate_rank = 0;
 };
 
 struct LayerSpec {
@@ -87,6 +105,21 @@ struct LayerSpec {
     ScanSpec scan;               // SSM_SCAN (heads and vdim above apply too)
     RouteSpec route;             // MOE_GLU
     bool ff_bias = false;        // GLU: every projection has a bias vector
+    // ---- mechanisms added with the Savidra family; every one is off at its default ----
+    bool token_shift = false;    // the mixer reads h_t = x_t + (x_{t-1} - x_t) * mu (per channel, x_{-1} = 0) instead of x_t; x_{t-1} is sequence state
+    int conv = 0;                // > 0: q, k and v pass a causal per-channel convolution of this many taps right after their projection
+                                 // (attention: no activation; DELTA_RULE: SiLU); the last conv - 1 projected rows are sequence state
+    bool qkv_bias = false;       // attention: q, k, v and the output projection have bias vectors
+    bool head_temp = false;      // attention: the scores of head h are multiplied by a learned number per head
+    bool talking = false;        // attention: after the softmax the heads' weights are mixed, w_h <- sum_g M[h, g] w_g, before head h applies
+                                 // them to the values of its own key / value head
+    bool sink = false;           // attention: the softmax denominator also holds exp(sink_h), a learned number per head without key or value
+    int v_first = -1;            // attention: >= 0 and != this layer: v <- (1 - lambda) v + lambda v', v' the values layer v_first computed for the
+                                 // same token (lambda a learned number); == this layer: the layer only publishes its values
+    DeltaSpec delta;             // DELTA_RULE (heads, kv_heads, dim, vdim and conv above apply too)
+    std::vector<LayerSpec> branches;     // BRANCHES: the mixers (their form, ff and token_shift are unused)
+    std::vector<float> branch_scale;     // BRANCHES: the weight of each branch's output in the sum
+    int cache_slot = -1;         // set when the model is finalized: which entry of the model's per-mixer cache table holds this mixer's rows
 };
 
 }}  // namespace nt::b200

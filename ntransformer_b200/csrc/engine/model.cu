@@ -81,9 +81,15 @@ Model::~Model() {
                     (void*)lat_.ku, (void*)lat_.vu})
         if (p) cudaFree(p);
     if (moe_offsets_host_) cudaFreeHost(moe_offsets_host_);
-    for (LayerWeights& L : layers_)
-        for (void* p : {(void*)L.e_up_tab, (void*)L.e_down_tab, (void*)L.rot_freq, (void*)L.e_gate_tab, (void*)L.conv_state, (void*)L.ssm_state}) if (p) cudaFree(p);
-    for (void* p : {(void*)dec_.y, (void*)dec_.t[0], (void*)dec_.t[1], (void*)dec_.t[2], (void*)dec_.t[3], (void*)dec_.t[4]}) if (p) cudaFree(p);
+    auto free_layer = [](LayerWeights& L) {
+        for (void* p : {(void*)L.e_up_tab, (void*)L.e_down_tab, (void*)L.rot_freq, (void*)L.e_gate_tab, (void*)L.conv_state, (void*)L.ssm_state, (void*)L.shift_state,
+                        (void*)L.q_conv_state, (void*)L.k_conv_state, (void*)L.v_conv_state, (void*)L.delta_state}) if (p) cudaFree(p);
+    };
+    for (LayerWeights& L : layers_) {
+        free_layer(L);
+        for (LayerWeights& b : L.branch) free_layer(b);
+    }
+    for (void* p : {(void*)dec_.y, (void*)dec_.t[0], (void*)dec_.t[1], (void*)dec_.t[2], (void*)dec_.t[3], (void*)dec_.t[4], (void*)dec_.wide, (void*)pf_.wide}) if (p) cudaFree(p);
     if (argmax_host_) cudaFreeHost(argmax_host_);
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -118,7 +124,7 @@ void Model::init(const ModelConfig& cfg, int tp_rank, int tp_size) {
 bool Model::set_tensor(const std::string& name, const void* ptr, DType dt, size_t pitch) {
     if (cfg_.layer_spec()) {
         for (const TensorBinding& b : family_->tensors(cfg_))
-            if (b.name == name) return bind_slot(b.slot, b.layer, ptr, dt, b.rows, b.cols, pitch, b.index);
+            if (b.name == name) return bind_slot(b.slot, b.layer, ptr, dt, b.rows, b.cols, pitch, b.index, b.branch);
         return false;
     }
     const int hidden = cfg_.hidden_size, hd = cfg_.head_dim;
@@ -407,8 +413,8 @@ bool Model::finalize() {
 
 void Model::clear_kv() {
     if (cfg_.layer_spec()) {
-        for (int i = 0; i < cfg_.n_layers; i++) {
-            const LayerSpec& L = cfg_.layers[(size_t)i];
+        for (int i = 0; i < (int)kcs_.size(); i++) {
+            const LayerSpec& L = slot_spec(i);
             const size_t es = dtype_size(cache_dt_);
             if (!cache_owned_[(size_t)i]) continue;
             (void)L;
@@ -431,6 +437,8 @@ size_t Model::weight_bytes() const {
             const LayerWeights& L = layer_weights(i);
             b += L.wq.bytes() + L.wk.bytes() + L.wv.bytes() + L.wo.bytes() + L.gate.bytes() + L.up.bytes() + L.down.bytes();
             b += L.w_dq.bytes() + L.w_uq.bytes() + L.w_dkv.bytes() + L.w_uk.bytes() + L.w_uv.bytes() + L.ssm_in.bytes() + L.side_gate.bytes() + L.side_proj.bytes();
+            for (const LayerWeights& m : L.branch)
+                b += m.wq.bytes() + m.wk.bytes() + m.wv.bytes() + m.wo.bytes() + m.d_beta.bytes() + m.d_a1.bytes() + m.d_a2.bytes() + m.d_g1.bytes() + m.d_g2.bytes();
             if (cfg_.layers[(size_t)i].ff_kind == FfKind::MOE_GLU && cfg_.layers[(size_t)i].ff > 0)
                 b += (size_t)cfg_.layers[(size_t)i].experts * cfg_.hidden_size * 4 +
                      (size_t)cfg_.layers[(size_t)i].top * (L.e_gate[0].bytes() + L.e_up[0].bytes() + L.e_down[0].bytes());
@@ -454,6 +462,10 @@ size_t Model::bytes_per_token(int ctx) const {
             cache_row_widths(L.kv_from >= 0 ? L.kv_from : i, kw, vw);
             b += (size_t)std::min(ctx, L.chunk > 0 ? L.chunk : (L.window > 0 ? L.window + L.keep_first : ctx)) * (kw + vw) * dtype_size(cache_dt_);
             if (L.mixer == MixerKind::SSM_SCAN) b += (size_t)2 * L.heads * L.vdim * L.scan.state * 4;      // the state is read and written
+            for (const LayerSpec& m : L.branches) {
+                if (m.mixer == MixerKind::DELTA_RULE) b += (size_t)2 * m.heads * m.vdim * m.dim * 4;
+                else if (m.cache_slot >= 0) { cache_row_widths(m.cache_slot, kw, vw); b += (size_t)ctx * (kw + vw) * dtype_size(cache_dt_); }
+            }
         }
         return b;
     }

@@ -68,6 +68,21 @@ struct LayerWeights {
     // per-layer token input: gate [side_dim, width], projection [width, side_dim], gain [width]
     Weight side_gate, side_proj;
     const float* side_norm = nullptr;
+    // token shift: per-channel blend (F32) and the sequence's carried row [width] (owned)
+    const float* shift_mu = nullptr;
+    float* shift_state = nullptr;
+    // attention options: projection biases, short-convolution taps [channels, taps] of q, k, v and the sequence's last taps - 1 inputs of
+    // each (owned), per-head score multiplier, head-mixing matrix [heads, heads], per-head sink, value-blend weight (all F32)
+    const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *o_bias = nullptr, *q_conv = nullptr, *k_conv = nullptr, *v_conv = nullptr;
+    float *q_conv_state = nullptr, *k_conv_state = nullptr, *v_conv_state = nullptr;
+    const float *head_temp = nullptr, *talk = nullptr, *sink = nullptr, *v_mix = nullptr;
+    // gated delta rule (DeltaSpec): beta projection, the two low-rank pairs (decay, output gate), decay bias [heads * dim], log decay rate
+    // [heads], output-norm gain [vdim]; the sequence's matrix state [heads, vdim, dim] in F32 (owned)
+    Weight d_beta, d_a1, d_a2, d_g1, d_g2;
+    const float *d_dt_bias = nullptr, *d_a_log = nullptr, *d_norm = nullptr;
+    float* delta_state = nullptr;
+    // MixerKind::BRANCHES: each branch's tensors and state
+    std::vector<LayerWeights> branch;
 };
 
 class Model {
@@ -139,14 +154,25 @@ public:
 private:
     // ---- layer-spec families (engine/model_spec.cu) ----
     const LayerWeights& layer_weights(int i) const { const int j = cfg_.layer_spec() ? cfg_.layers[(size_t)i].weights_of : -1; return layers_[(size_t)(j >= 0 ? j : i)]; }
-    bool bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch, int index = 0);
+    bool bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch, int index = 0, int branch = -1);
     // STREAMS block form: one decoded token / a chunk of prompt rows
     void layer_streams_token(int i, cudaStream_t s);
     void layer_streams_rows(int i, int T, int p0, cudaStream_t s);
     MoeWeights moe_of(int i, bool with_shared) const;
     // POST_NORM block form (latent attention / state-space scan mixers, biased or routed gated feed-forward, per-layer token input):
     // T rows at positions base.. (base = *pos_dev when given, else p0); T == 1 with pos_dev is the captured decode step.
-    struct RowBufs { float *x = nullptr, *y = nullptr, *t[5] = {nullptr, nullptr, nullptr, nullptr, nullptr}; };
+    struct RowBufs { float *x = nullptr, *y = nullptr, *t[5] = {nullptr, nullptr, nullptr, nullptr, nullptr}; float* wide = nullptr; };
+    // SUM_NORM block form (token shift, attention with per-head norm / convolutions / sink / mixed heads / blended values, the gated
+    // delta rule, mixers side by side): engine/model_sumnorm.cu.  Same conventions as layer_postnorm.
+    void layer_sumnorm(int i, int T, const int* pos_dev, int p0, const RowBufs& B, cudaStream_t s);
+    bool finalize_sumnorm_layer(int i);
+    bool finalize_mixer_state(LayerSpec& S, LayerWeights& M, int layer);   // states, frequency table and cache slot of one attention / delta mixer
+    size_t sumnorm_scratch_width() const;     // floats per row of RowBufs::wide
+    struct MixerBufs;
+    void mixer_attention_rows(int layer, const LayerSpec& S, const LayerWeights& L, const MixerBufs& b, float* y, int T, const int* pos_dev, int p0, cudaStream_t s);
+    void mixer_delta_rows(const LayerSpec& S, const LayerWeights& L, const MixerBufs& b, float* y, int T, const int* pos_dev, int p0, cudaStream_t s);
+    const LayerSpec& slot_spec(int slot) const { return *slot_spec_[(size_t)slot]; }
+    std::vector<const LayerSpec*> slot_spec_;   // the mixer behind every entry of kcs_ / vcs_: the layers first, then the branches that keep rows
     void layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev, int p0, const RowBufs& B, cudaStream_t s);
     void rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s);      // C = A . W^T: GEMV for one row, else spec_gemm
     size_t row_scratch_width() const;         // widest intermediate row of any POST_NORM layer
@@ -251,6 +277,7 @@ private:
         void *moe_ws2 = nullptr;                       // gated tensor-core experts: the split of act(gate) * up, input of the down GEMMs
         float *gate_rows = nullptr;                    // gated experts: W_gate h of the grouped rows [T*top, ff]
         float *wt = nullptr, *sgate = nullptr, *act_rows = nullptr, *y_rows = nullptr;   // weights [T, top], shared gate [T], grouped rows [T*top, ff | width]
+        float *wide = nullptr;                         // SUM_NORM: the mixers' intermediates [T, sumnorm_scratch_width()]
     } pf_;
     // Prompts shorter than this replay token by token through the decode chain (exact-integer GEMVs); longer ones take the batched
     // tensor-core prefill, whose F32 accumulation inside the tensor cores truncates once per 16-deep MMA step: ~1e-5..1e-4 per GEMM,

@@ -7,7 +7,7 @@
 namespace nt { namespace b200 {
 
 const std::vector<const ModelFamily*>& model_families() {
-    static const std::vector<const ModelFamily*> all = {zelunex_family(), vebotar_family(), tanolorn_family()};
+    static const std::vector<const ModelFamily*> all = {zelunex_family(), vebotar_family(), tanolorn_family(), savidra_family()};
     return all;
 }
 
@@ -17,7 +17,8 @@ bool slot_is_f32_table(TensorSlot s) {
         case TensorSlot::GATE: case TensorSlot::UP: case TensorSlot::DOWN: case TensorSlot::EXPERT_UP: case TensorSlot::EXPERT_DOWN:
         case TensorSlot::SHARED_UP: case TensorSlot::SHARED_DOWN: case TensorSlot::EXPERT_GATE:
         case TensorSlot::W_DQ: case TensorSlot::W_UQ: case TensorSlot::W_DKV: case TensorSlot::W_UK: case TensorSlot::W_UV:
-        case TensorSlot::SSM_IN: case TensorSlot::SIDE_EMBED: case TensorSlot::SIDE_GATE: case TensorSlot::SIDE_PROJ: return false;
+        case TensorSlot::SSM_IN: case TensorSlot::SIDE_EMBED: case TensorSlot::SIDE_GATE: case TensorSlot::SIDE_PROJ:
+        case TensorSlot::DELTA_BETA: case TensorSlot::DELTA_A1: case TensorSlot::DELTA_A2: case TensorSlot::DELTA_G1: case TensorSlot::DELTA_G2: return false;
         default: return true;
     }
 }

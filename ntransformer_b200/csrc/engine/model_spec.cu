@@ -41,7 +41,7 @@ bool Model::load(const std::string& path, int max_context) {
     return load_gguf(path, max_context);
 }
 
-bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch, int index) {
+bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch, int index, int branch) {
     auto W = [&](Weight& w) {
         if (!dense_dtype(dt)) return false;
         w.ptr = ptr; w.dtype = dt; w.rows = rows; w.cols = cols; w.pitch = pitch ? pitch : dtype_row_size(dt, (size_t)cols); w.owned = false;
@@ -53,8 +53,35 @@ bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int
     if (slot == TensorSlot::OUT_NORM) return V(out_norm_);
     if (slot == TensorSlot::SIDE_EMBED) return W(side_embd_);
     if (layer < 0 || layer >= cfg_.n_layers) return false;
-    LayerWeights& L = layers_[(size_t)layer];
+    LayerWeights* Lp = &layers_[(size_t)layer];
+    if (branch >= 0) {                      // a tensor of one of the mixers that sit side by side
+        const size_t nb = cfg_.layers[(size_t)layer].branches.size();
+        if ((size_t)branch >= nb) return false;
+        if (Lp->branch.size() != nb) Lp->branch.assign(nb, LayerWeights{});
+        Lp = &Lp->branch[(size_t)branch];
+    }
+    LayerWeights& L = *Lp;
     switch (slot) {
+        case TensorSlot::SHIFT_MU: return V(L.shift_mu);
+        case TensorSlot::Q_BIAS: return V(L.q_bias);
+        case TensorSlot::K_BIAS: return V(L.k_bias);
+        case TensorSlot::V_BIAS: return V(L.v_bias);
+        case TensorSlot::O_BIAS: return V(L.o_bias);
+        case TensorSlot::Q_CONV: return V(L.q_conv);
+        case TensorSlot::K_CONV: return V(L.k_conv);
+        case TensorSlot::V_CONV: return V(L.v_conv);
+        case TensorSlot::HEAD_TEMP: return V(L.head_temp);
+        case TensorSlot::TALK: return V(L.talk);
+        case TensorSlot::SINK: return V(L.sink);
+        case TensorSlot::V_MIX: return V(L.v_mix);
+        case TensorSlot::DELTA_BETA: return W(L.d_beta);
+        case TensorSlot::DELTA_A1: return W(L.d_a1);
+        case TensorSlot::DELTA_A2: return W(L.d_a2);
+        case TensorSlot::DELTA_G1: return W(L.d_g1);
+        case TensorSlot::DELTA_G2: return W(L.d_g2);
+        case TensorSlot::DELTA_DT_BIAS: return V(L.d_dt_bias);
+        case TensorSlot::DELTA_A_LOG: return V(L.d_a_log);
+        case TensorSlot::DELTA_NORM: return V(L.d_norm);
         case TensorSlot::NORM1: return V(L.attn_norm);
         case TensorSlot::NORM2: return V(L.ffn_norm);
         case TensorSlot::Q_NORM: return V(L.q_norm);
@@ -126,6 +153,15 @@ bool Model::load_dir(const std::string& dir, int max_context) {
     cfg.print();
     SafeTensorsFile f;
     if (!f.open(dir + "/model.safetensors")) return false;
+    if (fam->sizes_from_tensors) {          // sizes only a tensor's shape gives
+        std::string err;
+        const TensorShapeFn shape_of = [&](const std::string& name, std::vector<int64_t>& shape) {
+            const SafeTensorInfo* ti = f.find(name);
+            if (ti) shape = ti->shape;
+            return ti != nullptr;
+        };
+        if (!fam->sizes_from_tensors(cfg, shape_of, err)) { fprintf(stderr, "model: %s\n", err.c_str()); return false; }
+    }
     init(cfg, 0, 1);
     const std::vector<TensorBinding> plan = fam->tensors(cfg_);
     struct Job { const SafeTensorInfo* ti; const TensorBinding* b; size_t off; DType dst; };
@@ -134,8 +170,8 @@ bool Model::load_dir(const std::string& dir, int max_context) {
     for (const TensorBinding& b : plan) {
         const SafeTensorInfo* ti = f.find(b.name);
         if (!ti) { fprintf(stderr, "model: tensor not found: %s\n", b.name.c_str()); return false; }
-        const bool vec = b.rows == 1 && ti->shape.size() == 1;
-        if (!dense_dtype(ti->dtype) || !(vec ? ti->shape[0] == b.cols : (ti->shape.size() == 2 && ti->shape[0] == b.rows && ti->shape[1] == b.cols))) {
+        const bool vec = b.rows == 1 && ti->shape.size() == 1, scalar = b.rows == 1 && b.cols == 1 && ti->shape.empty();
+        if (!dense_dtype(ti->dtype) || !(scalar || (vec ? ti->shape[0] == b.cols : (ti->shape.size() == 2 && ti->shape[0] == b.rows && ti->shape[1] == b.cols)))) {
             fprintf(stderr, "model: tensor %s does not have the shape the configuration needs [%d x %d]\n", b.name.c_str(), b.rows, b.cols);
             return false;
         }
@@ -167,7 +203,7 @@ bool Model::load_dir(const std::string& dir, int max_context) {
             dense_to_f32(reinterpret_cast<float*>(base + j.off), dev_stage, j.ti->dtype, n, st);
         }
         NT_CUDA_CHECK(cudaStreamSynchronize(st));          // the staging buffers are reused by the next tensor
-        if (!bind_slot(j.b->slot, j.b->layer, base + j.off, j.dst, j.b->rows, j.b->cols, 0, j.b->index)) { fprintf(stderr, "model: cannot bind %s\n", j.b->name.c_str()); ok = false; break; }
+        if (!bind_slot(j.b->slot, j.b->layer, base + j.off, j.dst, j.b->rows, j.b->cols, 0, j.b->index, j.b->branch)) { fprintf(stderr, "model: cannot bind %s\n", j.b->name.c_str()); ok = false; break; }
     }
     cudaFreeHost(host);
     cudaFree(dev_stage);
@@ -186,6 +222,11 @@ bool Model::finalize_spec() {
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerSpec& S = cfg_.layers[(size_t)i];
         const LayerWeights& L = layer_weights(i);
+        if (S.form == BlockForm::SUM_NORM) {
+            if (!finalize_sumnorm_layer(i)) return false;
+            ffmax = std::max(ffmax, S.ff);
+            continue;
+        }
         if (S.form == BlockForm::POST_NORM) {
             LayerWeights& M = layers_[(size_t)i];
             bool ok = L.attn_norm && L.wo.ptr;
@@ -292,6 +333,12 @@ bool Model::finalize_spec() {
         fold(out_norm_);
         for (LayerWeights& L : layers_) { fold(L.attn_norm); fold(L.ffn_norm); }
     }
+    if (cfg_.layers[0].form == BlockForm::SUM_NORM) {
+        const size_t m1 = row_scratch_width();
+        dec_.y = dmalloc<float>(m1);
+        for (float*& t : dec_.t) t = dmalloc<float>(m1);
+        dec_.wide = dmalloc<float>(sumnorm_scratch_width());
+    }
     if (cfg_.layers[0].form == BlockForm::POST_NORM) {
         const size_t m1 = row_scratch_width();
         dec_.y = dmalloc<float>(m1);
@@ -319,12 +366,19 @@ bool Model::finalize_spec() {
     }
     logits_ = dmalloc<float>(cfg_.vocab_size);
     NT_CUDA_CHECK(cudaMemset(logits_, 0, sizeof(float) * (size_t)cfg_.vocab_size));
-    kcs_.assign((size_t)cfg_.n_layers, nullptr);
-    vcs_.assign((size_t)cfg_.n_layers, nullptr);
-    cache_owned_.assign((size_t)cfg_.n_layers, 1);
+    // the cache table: one entry per layer, then one per mixer that sits beside another inside a layer and keeps rows of its own
+    slot_spec_.clear();
+    for (LayerSpec& S : cfg_.layers) { S.cache_slot = (int)slot_spec_.size(); slot_spec_.push_back(&S); }
+    for (LayerSpec& S : cfg_.layers)
+        for (LayerSpec& b : S.branches)
+            if (b.mixer != MixerKind::DELTA_RULE && b.mixer != MixerKind::SSM_SCAN) { b.cache_slot = (int)slot_spec_.size(); slot_spec_.push_back(&b); }
+    const int n_slots = (int)slot_spec_.size();
+    kcs_.assign((size_t)n_slots, nullptr);
+    vcs_.assign((size_t)n_slots, nullptr);
+    cache_owned_.assign((size_t)n_slots, 1);
     const size_t es = dtype_size(cache_dt_);
-    for (int i = 0; i < cfg_.n_layers; i++) {          // every layer RUN owns a cache, also one that borrows its tensors; not one that reads another's rows
-        const LayerSpec& S = cfg_.layers[(size_t)i];
+    for (int i = 0; i < n_slots; i++) {          // every layer RUN owns a cache, also one that borrows its tensors; not one that reads another's rows
+        const LayerSpec& S = slot_spec(i);
         if (S.kv_from >= 0) { kcs_[(size_t)i] = kcs_[(size_t)S.kv_from]; vcs_[(size_t)i] = vcs_[(size_t)S.kv_from]; cache_owned_[(size_t)i] = 0; continue; }
         size_t kw = 0, vw = 0;
         cache_row_widths(i, kw, vw);
@@ -362,6 +416,12 @@ void Model::step_body_spec(cudaStream_t s) {
         RowBufs B = dec_;
         B.x = hidden_;
         for (int i = 0; i < cfg_.n_layers; i++) layer_postnorm(i, 1, step_dev_, pos_dev, 0, B, s);
+        return;
+    }
+    if (cfg_.layers[0].form == BlockForm::SUM_NORM) {
+        RowBufs B = dec_;
+        B.x = hidden_;
+        for (int i = 0; i < cfg_.n_layers; i++) layer_sumnorm(i, 1, pos_dev, 0, B, s);
         return;
     }
     if (cfg_.layers[0].form == BlockForm::STREAMS) {
@@ -404,13 +464,15 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream_));
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, (void*)pf_.g, (void*)pf_.u, (void*)pf_.h, (void*)pf_.tmp,
                     pf_.ws, pf_.ws2, pf_.hws, (void*)pf_.tok, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt, (void*)pf_.sgate,
-                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws, pf_.moe_ws2, (void*)pf_.gate_rows})
+                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws, pf_.moe_ws2, (void*)pf_.gate_rows, (void*)pf_.wide})
         if (p) cudaFree(p);
-    pf_.moe_ws2 = nullptr;
+    pf_.moe_ws2 = nullptr; pf_.wide = nullptr;
     pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = pf_.g2 = pf_.gate_rows = nullptr; pf_.sel = pf_.work = nullptr; pf_.moe_ws = nullptr;
     const size_t T = (size_t)((tokens + 127) / 128 * 128), hidden = (size_t)cfg_.hidden_size;
     size_t qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1, mapmax = 1, topmax = 0, emax = 1, effmax = 1;
-    const bool post_form = cfg_.layers[0].form == BlockForm::POST_NORM;
+    const bool sum_form = cfg_.layers[0].form == BlockForm::SUM_NORM;
+    const bool post_form = cfg_.layers[0].form == BlockForm::POST_NORM || sum_form;       // both keep five scratch rows of the widest intermediate
+    if (sum_form) pf_.wide = dmalloc<float>(T * sumnorm_scratch_width());
     for (const LayerSpec& S : cfg_.layers) {
         if (post_form) {                  // five scratch rows of the widest intermediate; routed experts as below
             qmax = kmax = vmax = omax = ffmax = row_scratch_width();
@@ -449,6 +511,12 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
         const LayerWeights& L = layer_weights(i);
         for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.sh_up, &L.sh_down, &L.w_dq, &L.w_uq, &L.w_dkv, &L.ssm_in, &L.side_gate, &L.side_proj})
             any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
+        for (const LayerWeights& b : L.branch)
+            for (const Weight* w : {&b.wq, &b.wk, &b.wv, &b.wo, &b.d_beta, &b.d_a1, &b.d_a2, &b.d_g1, &b.d_g2}) {
+                any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
+                ffmax = std::max(ffmax, (size_t)w->cols);          // the split workspace holds the widest GEMM input
+            }
+        ffmax = std::max(ffmax, (size_t)L.wo.cols);
     }
     if (post_form && any_tc) {            // one split workspace: rows_matmul splits its input right before the GEMM
         pf_.ws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)std::max(hidden, ffmax)));
@@ -497,11 +565,13 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
         NT_CUDA_CHECK(cudaMemcpyAsync(pf_.tok, tokens + c0, sizeof(int) * (size_t)T, cudaMemcpyHostToDevice, s));
         embed_rows(pf_.x, embd_.ptr, embd_.dtype, pf_.tok, T, hidden, s);
         const bool streams_form = cfg_.layers[0].form == BlockForm::STREAMS, post_form = cfg_.layers[0].form == BlockForm::POST_NORM;
+        const bool sum_form = cfg_.layers[0].form == BlockForm::SUM_NORM;
         if (streams_form) streams_spread(pf_.xs, pf_.x, cfg_.embed_scale, T, n_streams(), hidden, s);
         RowBufs rb;
-        rb.x = pf_.x; rb.y = pf_.tmp; rb.t[0] = pf_.q; rb.t[1] = pf_.k; rb.t[2] = pf_.v; rb.t[3] = pf_.attn; rb.t[4] = pf_.g;
+        rb.x = pf_.x; rb.y = pf_.tmp; rb.t[0] = pf_.q; rb.t[1] = pf_.k; rb.t[2] = pf_.v; rb.t[3] = pf_.attn; rb.t[4] = pf_.g; rb.wide = pf_.wide;
         for (int i = 0; i < cfg_.n_layers; i++) {
             if (streams_form) { layer_streams_rows(i, T, p0, s); continue; }
+            if (sum_form) { layer_sumnorm(i, T, nullptr, p0, rb, s); continue; }
             if (post_form) { layer_postnorm(i, T, pf_.tok, nullptr, p0, rb, s); continue; }
             const LayerSpec& S = cfg_.layers[(size_t)i];
             const LayerWeights& L = layer_weights(i);
@@ -680,8 +750,8 @@ void Model::layer_streams_rows(int i, int T, int p0, cudaStream_t s) {
 // ---- BlockForm::POST_NORM layers (latent attention, state-space scan, biased / routed gated feed-forward, per-layer token input) ----
 
 void Model::cache_row_widths(int i, size_t& k, size_t& v) const {
-    const LayerSpec& S = cfg_.layers[(size_t)i];
-    if (S.mixer == MixerKind::SSM_SCAN) { k = v = 0; return; }                                             // a state, no rows
+    const LayerSpec& S = slot_spec(i);
+    if (S.mixer == MixerKind::SSM_SCAN || S.mixer == MixerKind::DELTA_RULE || S.mixer == MixerKind::BRANCHES) { k = v = 0; return; }      // a state, no rows (branches own theirs)
     if (S.mixer == MixerKind::ATTN_LATENT) { k = (size_t)S.latent.kv_rank + S.latent.rot_dim; v = 0; return; }   // [latent | rotated key part]
     k = (size_t)S.kv_heads * S.maps * S.dim;
     v = (size_t)S.kv_heads * S.vdim;
@@ -690,6 +760,7 @@ void Model::cache_row_widths(int i, size_t& k, size_t& v) const {
 size_t Model::row_scratch_width() const {
     size_t m = (size_t)cfg_.hidden_size;
     for (const LayerSpec& S : cfg_.layers) {
+        if (S.form == BlockForm::SUM_NORM) { m = std::max(m, (size_t)S.ff); continue; }      // the mixers' intermediates live in RowBufs::wide
         if (S.mixer == MixerKind::ATTN_LATENT) {
             const LatentSpec& A = S.latent;
             m = std::max({m, (size_t)A.q_rank, (size_t)A.kv_rank + A.rot_dim, (size_t)S.heads * (S.dim + A.rot_dim), (size_t)S.heads * (A.kv_rank + A.rot_dim),

@@ -130,7 +130,9 @@ bool sample_topk(float* logits_dev, int n, float temperature, int top_k, float t
 // ---- dense.cu / attention_window.cu: kernels of the layer-spec model families (dense F32 / F16 / BF16 weights, F32 activations) ----
 enum DenseEpilogue { DENSE_STORE = 0, DENSE_ADD = 1, DENSE_SCALED_ADD = 2 /* y[r] += alpha * row_scale[r] * (W.x)[r]; row_scale may be null */,
                      DENSE_SWIGLU = 3 /* y0 = silu(W0.x) * (W1.x) */, DENSE_GEGLU = 4 /* y0 = gelu_tanh(W0.x) * (W1.x) */,
-                     DENSE_STREAMS = 5 /* one matrix; its output enters the residual streams: StreamsIO::X_out, y is not written */ };
+                     DENSE_STREAMS = 5 /* one matrix; its output enters the residual streams: StreamsIO::X_out, y is not written */,
+                     DENSE_REGLU = 6 /* y0 = relu(W0.x) * (W1.x) */ };
+constexpr int DENSE_MAX_MATS = 12;      // matrices of one gemv_dense launch
 // Residual streams [S, n] of ONE token folded into a GEMV (decode).  Prologue (X_in given): the activation vector is
 // x[i] = sum_s a[s] * X_in[s * K + i] (a == null: the plain sum) instead of the x argument.  Epilogue DENSE_STREAMS: with v = (W.x)[r],
 // X_out[t * N + r] <- sum_s M[s * S + t] * X_out[s * N + r] + b[t] * v for every t (row r is owned by one warp, so the update is race-free).
@@ -140,14 +142,14 @@ struct StreamsIO {
     int S = 0;
 };
 bool dense_dtype(DType dt);
-// Up to 3 matrices of one dense dtype sharing the activation vector x[K] (GemvMat::y: each matrix's output rows).
+// Up to DENSE_MAX_MATS matrices of one dense dtype sharing the activation vector x[K] (GemvMat::y: each matrix's output rows).
 // norm_w: the kernel's prologue first replaces x by x / sqrt(mean(x^2) + eps) * norm_w (the block's RMS norm, recomputed per CTA).
 void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s,
                 const float* norm_w = nullptr, float eps = 0.f, const StreamsIO* sio = nullptr);
 // C[T,N] (ep)= A[T,K] . W[N,K]^T in true FP32 on CUDA cores (store / add / scaled-add; row_scale indexes N).
 void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pitch, int T, int N, int K, DenseEpilogue ep,
                 const float* row_scale, float alpha, cudaStream_t s);
-void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s);      // out = act(gate) * up
+void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s, bool relu = false);      // out = act(gate) * up (SiLU, tanh-GELU or ReLU)
 void scaled_add_rows(float* x, const float* y, const float* row_scale, float alpha, int rows, int cols, cudaStream_t s);   // x[r,c] += alpha * row_scale[c] * y[r,c]
 void dense_to_f32(float* out, const void* in, DType dt, size_t n, cudaStream_t s);
 struct WindowAttn {
@@ -159,6 +161,9 @@ struct WindowAttn {
                                        // every map is an attention of its own over the head's values; out [tokens, heads*maps*vdim]
     int k_stride = 0, v_stride = 0;    // elements between consecutive positions' key / value rows; 0: packed (kv_heads*maps*dim, kv_heads*vdim).
                                        // With strides the two caches may be one buffer (values = a slice of the key rows: latent attention)
+    const float* sink = nullptr;       // [heads] (device): exp(sink[h]) joins head h's softmax denominator; it has no key and no value
+    int joint_v = 0;                   // 1: every query head sums ONE value row per key, vdim wide, at the start of the key's value row (whatever its
+                                       // key head): with vdim = kv_heads * (a head's width) each head's weights are applied to every value head at once
 };
 // Q [tokens, heads*dim] at positions base.. (base = *pos_dev when pos_dev is given, else p0); caches [max_seq, kv_heads*dim|vdim] of
 // cache_dt (F32 or BF16) that already hold the rows of these tokens; out [tokens, heads*vdim].
@@ -279,6 +284,53 @@ void ssm_gate_norm(float* out, const float* y, const float* u, int ld, int z_col
 void add_rmsnorm_rows(float* x, const float* y, const float* gain, const float* bias, int rows, int width, float eps, cudaStream_t s);
 void glu_bias_mul(float* out, const float* gate, const float* up, const float* gate_bias, const float* up_bias, int rows, int cols, bool gelu, cudaStream_t s);
 void side_gate_rows(float* g, const void* E, DType dt, int e_cols, int col0, const int* tokens_dev, int rows, int dim, cudaStream_t s);
+
+// ---- short_conv.cu / delta_rule.cu / sumnorm.cu / attention_heads.cu: mechanisms added with the fourth layer-spec family ----
+// Short causal convolutions on projected rows, several projections ("segments") per launch.  u [T, ld], channel c at column col0 + c;
+// out [T, out_ld] (not the rows it reads); w [ch, taps], the last tap is the current token's; in_bias [ch] or null is added to every input
+// row (zeros before the sequence's start stay zeros); state [taps - 1, ch]: the sequence's last inputs, read unless the step starts at
+// position 0, rewritten with the step's last inputs; act: 0 none, 1 SiLU.
+struct ConvSeg {
+    const float* u = nullptr; int ld = 0, col0 = 0;
+    float* out = nullptr; int out_ld = 0;
+    int ch = 0, taps = 0;
+    const float* w = nullptr; const float* in_bias = nullptr;
+    float* state = nullptr;
+    int act = 0;
+};
+constexpr int SHORT_CONV_MAX_SEGS = 6;
+void short_conv(const ConvSeg* segs, int n, int T, const int* pos_dev, int p0, cudaStream_t s);
+// Gated delta rule (engine/layer_spec.h DeltaSpec).  prep, in place: q, k [T, kv_heads, dim] to unit length per head (q also times dim^-1/2);
+// a [T, heads, dim] <- exp(-exp(A_log_h) softplus(a + dt_bias)); beta [T, heads] <- sigmoid(beta); qk [T, kv_heads] = <q, k>.
+// rows: out [T, heads, vdim] from the recurrence over the step's rows; state [heads, vdim, dim] is read unless the step starts at
+// position 0 and written back.  gate_norm: out = o / sqrt(mean_v o^2 + eps) * gain[v] * sigmoid(gate_raw), per head.
+constexpr int DELTA_MAX_DIM = 256;
+void delta_prep(float* q, float* k, float* a, float* beta, float* qk, const float* dt_bias, const float* A_log, int T, int heads, int kv_heads, int dim,
+                cudaStream_t s);
+void delta_rule_rows(float* out, const float* q, const float* k, const float* v, const float* a, const float* beta, const float* qk, float* state, int T,
+                     int heads, int kv_heads, int dim, int vdim, const int* pos_dev, int p0, cudaStream_t s);
+void delta_gate_norm(float* out, const float* o, const float* gate_raw, const float* gain, float eps, int T, int heads, int vdim, cudaStream_t s);
+// Block form that norms the residual sum: x[t] <- rms(a x[t] + s1 (y1[t] + b1) + s2 y2[t]) * gain (y2, b1 may be null).  h_next (one row
+// only): also the next mixer's shifted input h = x' + (carried - x') mu, after which x' becomes the carried row.
+void sum_rmsnorm_rows(float* x, float a, const float* y1, float s1, const float* b1, const float* y2, float s2, const float* gain, int rows, int width, float eps,
+                      cudaStream_t s, float* h_next = nullptr, const float* mu = nullptr, float* carried = nullptr, const int* pos_dev = nullptr, int p0 = 0);
+// Token shift: h[t] = x[t] + (x[t-1] - x[t]) mu; x[-1] is the carried row (zeros when the step starts at position 0), which then becomes the step's last row.
+void token_shift_rows(float* h, const float* x, const float* mu, float* carried, int rows, int width, const int* pos_dev, int p0, cudaStream_t s);
+// Per-head query / key norm, rotation from a frequency table, per-head query multiplier, value blend, cache write (attention_heads.cu).
+struct HeadPrep {
+    int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+    const float* q_gain = nullptr; const float* k_gain = nullptr; float eps = 0.f;      // [dim] each; null: no norm
+    int rot_dims = 0, interleaved = 0; const float* freq = nullptr;                      // [rot_dims / 2] angular frequencies (device)
+    const float* temp = nullptr;            // [heads] or null
+    const float* v_lambda = nullptr;        // one number (device); used with v_first
+    const float* v_first = nullptr;         // [T, kv_heads * vdim] F32 or null
+    float* v_publish = nullptr;             // [T, kv_heads * vdim] F32 or null: receives the values as projected
+};
+void head_prep(float* Q, const float* K, const float* V, const HeadPrep& p, void* kc, void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0,
+               cudaStream_t s);
+// out [T, heads, vdim] = sum_g M[h, g] A(t, g, kv(h), :), A addressed as A + t * t_stride + g * g_stride + c * c_stride.
+void talk_mix(float* out, const float* A, const float* M, int tokens, int heads, int kv_heads, int vdim, size_t t_stride, size_t g_stride, size_t c_stride,
+              cudaStream_t s);
 
 // Programmatic dependent launch (PDL): when enabled, kernels are launched with
 // cudaLaunchAttributeProgrammaticStreamSerialization so that a kernel's prologue (barrier init, TMA weight
