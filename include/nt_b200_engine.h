@@ -101,6 +101,23 @@ void nt_b200_ssm_gate_norm(float* out, const float* y, const float* u, int ld, i
 void nt_b200_add_rmsnorm_rows(float* x, const float* y, const float* gain, const float* bias, int rows, int width, float eps, void* stream);
 void nt_b200_glu_bias_mul(float* out, const float* gate, const float* up, const float* gate_bias, const float* up_bias, int rows, int cols, int gelu, void* stream);
 void nt_b200_side_gate_rows(float* g, const void* E, int dtype, int e_cols, int col0, const int* tokens_dev, int rows, int dim, void* stream);
+/* Kernels of the block that norms the residual sum, short convolutions with carried inputs, the gated delta rule, attention with per-head
+ * norm / sink / head-mixed weights (numerics tests).  Optional pointers may be null. */
+void nt_b200_short_conv(const void* const* u, void* const* out, const void* const* w, const void* const* in_bias, void* const* state, const int* ch, const int* taps,
+                        const int* act, int n_seg, int tokens, int p0, void* stream);
+void nt_b200_delta_prep(float* q, float* k, float* a, float* beta, float* qk, const float* dt_bias, const float* A_log, int tokens, int heads, int kv_heads, int dim,
+                        void* stream);
+void nt_b200_delta_rule_rows(float* out, const float* q, const float* k, const float* v, const float* a, const float* beta, const float* qk, float* state, int tokens,
+                             int heads, int kv_heads, int dim, int vdim, int p0, void* stream);
+void nt_b200_delta_gate_norm(float* out, const float* o, const float* gate_raw, const float* gain, float eps, int tokens, int heads, int vdim, void* stream);
+void nt_b200_sum_rmsnorm_rows(float* x, float a, const float* y1, float s1, const float* b1, const float* y2, float s2, const float* gain, int rows, int width, float eps,
+                              float* h_next, const float* mu, float* carried, int p0, void* stream);
+void nt_b200_token_shift_rows(float* h, const float* x, const float* mu, float* carried, int rows, int width, int p0, void* stream);
+void nt_b200_head_prep(float* Q, const float* K, const float* V, int heads, int kv_heads, int dim, int vdim, const float* q_gain, const float* k_gain, float eps,
+                       int rot_dims, int interleaved, const float* freq, const float* temp, const float* v_lambda, const float* v_first, float* v_publish, void* kc,
+                       void* vc, int cache_dtype, int tokens, int p0, void* stream);
+void nt_b200_attention_heads(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int max_seq, int heads, int kv_heads,
+                             int dim, int vdim, float scale, const float* sink, const float* talk, float* scratch, int one_pass, void* stream);
 /* router with sigmoid scores, a choice-only correction and a limit to the best runs of neighbouring experts; gated experts */
 void nt_b200_moe_route_scored(int* sel, float* wt, const float* h, const float* router, const float* correction, int experts, int top, int groups, int keep,
                               int width, int tokens, void* stream);

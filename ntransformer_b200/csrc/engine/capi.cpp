@@ -90,6 +90,15 @@ int nt_model_dir_describe(const char* dir, char* out, size_t cap) {
     if (!read_model_dir(dir, cfg, &fam)) return put("config.json rejected", -1);
     SafeTensorsFile f;
     if (!f.open(std::string(dir) + "/model.safetensors")) return put("model.safetensors rejected", -1);
+    if (fam->sizes_from_tensors) {
+        std::string err;
+        const TensorShapeFn shape_of = [&](const std::string& name, std::vector<int64_t>& shape) {
+            const SafeTensorInfo* ti = f.find(name);
+            if (ti) shape = ti->shape;
+            return ti != nullptr;
+        };
+        if (!fam->sizes_from_tensors(cfg, shape_of, err)) return put(err, -1);
+    }
     std::string text = std::string("architecture=") + fam->architecture + " vocab=" + std::to_string(cfg.vocab_size) + " width=" + std::to_string(cfg.hidden_size) +
                        " layers=" + std::to_string(cfg.n_layers) + " eps=" + std::to_string(cfg.norm_eps) + " mult=" + std::to_string(cfg.residual_mult) + "\n";
     for (size_t i = 0; i < cfg.layers.size(); i++) {
@@ -112,13 +121,28 @@ int nt_model_dir_describe(const char* dir, char* out, size_t cap) {
             text += std::string(" ff_kind=") + (L.ff == 0 ? "none" : L.ff_kind == FfKind::GLU ? "dense" : "moe") + " experts=" + std::to_string(L.experts) + " top=" +
                     std::to_string(L.top) + " route_groups=" + std::to_string(L.route.groups) + "/" + std::to_string(L.route.keep) + " side=" + std::to_string(cfg.side_dim);
         }
+        if (L.form == BlockForm::SUM_NORM) {
+            auto mixer_text = [](const LayerSpec& M) {
+                if (M.mixer == MixerKind::DELTA_RULE)
+                    return " delta(heads=" + std::to_string(M.heads) + " kv=" + std::to_string(M.kv_heads) + " dim=" + std::to_string(M.dim) + " vdim=" + std::to_string(M.vdim) +
+                           " conv=" + std::to_string(M.conv) + " ranks=" + std::to_string(M.delta.decay_rank) + "/" + std::to_string(M.delta.gate_rank) + ")";
+                return " attention(heads=" + std::to_string(M.heads) + " kv=" + std::to_string(M.kv_heads) + " dim=" + std::to_string(M.dim) + " vdim=" + std::to_string(M.vdim) +
+                       " rot=" + std::to_string(M.rot.dims) + " divide=" + std::to_string(M.rot.divide) + " conv=" + std::to_string(M.conv) + " bias=" + std::to_string(M.qkv_bias) +
+                       " temp=" + std::to_string(M.head_temp) + " talking=" + std::to_string(M.talking) + " sink=" + std::to_string(M.sink) + " v_first=" + std::to_string(M.v_first) + ")";
+            };
+            text += " skip=" + std::to_string(cfg.skip_scale) + " shift=" + std::to_string(L.token_shift);
+            if (L.mixer == MixerKind::BRANCHES)
+                for (size_t b = 0; b < L.branches.size(); b++) text += " " + std::to_string(L.branch_scale[b]) + " *" + mixer_text(L.branches[b]);
+            else text += mixer_text(L);
+        }
         text += "\n";
     }
     size_t n = 0;
     for (const TensorBinding& b : fam->tensors(cfg)) {
         const SafeTensorInfo* ti = f.find(b.name);
         if (!ti) return put("tensor not found: " + b.name, -1);
-        const bool ok = (b.rows == 1 && ti->shape.size() == 1) ? ti->shape[0] == b.cols : (ti->shape.size() == 2 && ti->shape[0] == b.rows && ti->shape[1] == b.cols);
+        const bool ok = (b.rows == 1 && b.cols == 1 && ti->shape.empty()) ||
+                        ((b.rows == 1 && ti->shape.size() == 1) ? ti->shape[0] == b.cols : (ti->shape.size() == 2 && ti->shape[0] == b.rows && ti->shape[1] == b.cols));
         if (!ok) return put("tensor " + b.name + " does not have the shape the configuration needs", -1);
         n++;
     }
@@ -299,6 +323,69 @@ void nt_b200_add_rmsnorm_rows(float* x, const float* y, const float* gain, const
 }
 void nt_b200_glu_bias_mul(float* out, const float* gate, const float* up, const float* gate_bias, const float* up_bias, int rows, int cols, int gelu, void* stream) {
     glu_bias_mul(out, gate, up, gate_bias, up_bias, rows, cols, gelu != 0, static_cast<cudaStream_t>(stream));
+}
+// ---- kernels of the sum-norm block, the short convolutions, the gated delta rule and attention with per-head options ----
+// Up to 6 segments: per segment u, out, w, in_bias (may be null), state (device pointers) and ch, taps, act (0 none, 1 SiLU); rows are packed (ld == ch).
+void nt_b200_short_conv(const void* const* u, void* const* out, const void* const* w, const void* const* in_bias, void* const* state, const int* ch, const int* taps,
+                        const int* act, int n_seg, int tokens, int p0, void* stream) {
+    ConvSeg segs[SHORT_CONV_MAX_SEGS];
+    NT_CHECK(n_seg >= 1 && n_seg <= SHORT_CONV_MAX_SEGS, "nt_b200_short_conv: 1..6 segments");
+    for (int i = 0; i < n_seg; i++) {
+        segs[i].u = static_cast<const float*>(u[i]); segs[i].ld = ch[i]; segs[i].out = static_cast<float*>(out[i]); segs[i].out_ld = ch[i]; segs[i].ch = ch[i];
+        segs[i].taps = taps[i]; segs[i].w = static_cast<const float*>(w[i]); segs[i].in_bias = static_cast<const float*>(in_bias[i]);
+        segs[i].state = static_cast<float*>(state[i]); segs[i].act = act[i];
+    }
+    short_conv(segs, n_seg, tokens, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_delta_prep(float* q, float* k, float* a, float* beta, float* qk, const float* dt_bias, const float* A_log, int tokens, int heads, int kv_heads, int dim,
+                        void* stream) {
+    delta_prep(q, k, a, beta, qk, dt_bias, A_log, tokens, heads, kv_heads, dim, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_delta_rule_rows(float* out, const float* q, const float* k, const float* v, const float* a, const float* beta, const float* qk, float* state, int tokens,
+                             int heads, int kv_heads, int dim, int vdim, int p0, void* stream) {
+    delta_rule_rows(out, q, k, v, a, beta, qk, state, tokens, heads, kv_heads, dim, vdim, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_delta_gate_norm(float* out, const float* o, const float* gate_raw, const float* gain, float eps, int tokens, int heads, int vdim, void* stream) {
+    delta_gate_norm(out, o, gate_raw, gain, eps, tokens, heads, vdim, static_cast<cudaStream_t>(stream));
+}
+// h_next / mu / carried may be null (no fused shift; it takes one row)
+void nt_b200_sum_rmsnorm_rows(float* x, float a, const float* y1, float s1, const float* b1, const float* y2, float s2, const float* gain, int rows, int width, float eps,
+                              float* h_next, const float* mu, float* carried, int p0, void* stream) {
+    sum_rmsnorm_rows(x, a, y1, s1, b1, y2, s2, gain, rows, width, eps, static_cast<cudaStream_t>(stream), h_next, mu, carried, nullptr, p0);
+}
+void nt_b200_token_shift_rows(float* h, const float* x, const float* mu, float* carried, int rows, int width, int p0, void* stream) {
+    token_shift_rows(h, x, mu, carried, rows, width, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+// q_gain / k_gain / freq / temp / v_lambda / v_first / v_publish may be null
+void nt_b200_head_prep(float* Q, const float* K, const float* V, int heads, int kv_heads, int dim, int vdim, const float* q_gain, const float* k_gain, float eps,
+                       int rot_dims, int interleaved, const float* freq, const float* temp, const float* v_lambda, const float* v_first, float* v_publish, void* kc,
+                       void* vc, int cache_dtype, int tokens, int p0, void* stream) {
+    HeadPrep p;
+    p.heads = heads; p.kv_heads = kv_heads; p.dim = dim; p.vdim = vdim; p.q_gain = q_gain; p.k_gain = k_gain; p.eps = eps; p.rot_dims = rot_dims;
+    p.interleaved = interleaved; p.freq = freq; p.temp = temp; p.v_lambda = v_lambda; p.v_first = v_first; p.v_publish = v_publish;
+    head_prep(Q, K, V, p, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, static_cast<cudaStream_t>(stream));
+}
+// Full causal grouped-query attention over cache rows with an optional per-head sink (null: none).  talk (null: none): [heads, heads], the
+// softmax weights are mixed across heads before head h applies them to its own value head; scratch [tokens, heads, kv_heads * vdim] is then needed.
+// one_pass != 0 (or kv_heads * vdim > 512 is not the case): every value head in one pass; else one pass per value head.
+void nt_b200_attention_heads(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int max_seq, int heads, int kv_heads,
+                             int dim, int vdim, float scale, const float* sink, const float* talk, float* scratch, int one_pass, void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const nt::DType dt = (nt::DType)cache_dtype;
+    WindowAttn a;
+    a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.scale = scale; a.sink = sink;
+    if (!talk) { attention_window(out, Q, kc, vc, dt, tokens, nullptr, p0, max_seq, a, s); return; }
+    a.joint_v = 1; a.v_stride = kv_heads * vdim;
+    if (one_pass) {
+        a.vdim = kv_heads * vdim;
+        attention_window(scratch, Q, kc, vc, dt, tokens, nullptr, p0, max_seq, a, s);
+        talk_mix(out, scratch, talk, tokens, heads, kv_heads, vdim, (size_t)heads * kv_heads * vdim, (size_t)kv_heads * vdim, (size_t)vdim, s);
+        return;
+    }
+    for (int c = 0; c < kv_heads; c++)
+        attention_window(scratch + (size_t)c * tokens * heads * vdim, Q, kc, static_cast<const uint8_t*>(vc) + (size_t)c * vdim * dtype_size(dt), dt, tokens, nullptr, p0,
+                         max_seq, a, s);
+    talk_mix(out, scratch, talk, tokens, heads, kv_heads, vdim, (size_t)heads * vdim, (size_t)vdim, (size_t)tokens * heads * vdim, s);
 }
 void nt_b200_side_gate_rows(float* g, const void* E, int dtype, int e_cols, int col0, const int* tokens_dev, int rows, int dim, void* stream) {
     side_gate_rows(g, E, (nt::DType)dtype, e_cols, col0, tokens_dev, rows, dim, static_cast<cudaStream_t>(stream));

@@ -24,6 +24,7 @@ template <typename T> T* dmalloc0(size_t n) {
     NT_CUDA_CHECK(cudaMemset(p, 0, std::max<size_t>(n, 1) * sizeof(T)));
     return p;
 }
+constexpr size_t kScratchSlack = 256;       // floats behind RowBufs::wide for the 16-byte alignment of the buffers carved from it
 GemvMat mat_of(const Weight& w, float* y) { GemvMat m; m.W = w.ptr; m.y = y; m.out = w.rows; m.dtype = w.dtype; m.row_pitch = w.pitch; return m; }
 
 // floats per row that one mixer's intermediates take in RowBufs::wide (see carve())
@@ -53,7 +54,7 @@ size_t Model::sumnorm_scratch_width() const {
         m = std::max(m, w);
         if (S.v_first >= 0) vf = std::max(vf, (size_t)S.kv_heads * S.vdim);
     }
-    return m + vf + 2 * (size_t)cfg_.hidden_size;          // + the published values of the step + the two branch outputs
+    return m + vf + 2 * (size_t)cfg_.hidden_size + kScratchSlack;          // + the published values of the step + the two branch outputs + alignment gaps
 }
 
 bool Model::finalize_mixer_state(LayerSpec& S, LayerWeights& M, int layer) {
@@ -161,8 +162,9 @@ void Model::layer_sumnorm(int i, int T, const int* pos_dev, int p0, const RowBuf
     float* h = S.token_shift ? B.t[0] : B.x;
     if (S.token_shift && (T > 1 || i == 0)) token_shift_rows(h, B.x, L.shift_mu, L.shift_state, T, hidden, pos_dev, p0, s);
     // ---- carve the mixers' rows: [published values | branch outputs y1, y2 | per mixer ...] ----
-    size_t off = 0;
-    auto take = [&](size_t w) { float* p = B.wide + off * (size_t)T; off += w; return p; };
+    // every buffer starts on 16 bytes (vector loads of the tiled kernels), whatever T is: at most 3 floats are skipped per buffer
+    size_t off = 0, cur = 0;
+    auto take = [&](size_t w) { cur = (cur + 3) & ~(size_t)3; float* p = B.wide + cur; cur += w * (size_t)T; off += w; return p; };
     size_t vf = 0;
     for (const LayerSpec& Z : cfg_.layers) if (Z.v_first >= 0) vf = std::max(vf, (size_t)Z.kv_heads * Z.vdim);
     float* published = take(vf);
@@ -210,7 +212,7 @@ void Model::layer_sumnorm(int i, int T, const int* pos_dev, int p0, const RowBuf
             b.pub = published;
         }
     }
-    NT_CHECK(off <= sumnorm_scratch_width(), "layer_sumnorm: scratch rows overrun");
+    NT_CHECK(off <= sumnorm_scratch_width() && cur <= sumnorm_scratch_width() * (size_t)T, "layer_sumnorm: scratch rows overrun");
     // ---- projections (one launch for a decoded token), convolutions (one launch), then each mixer ----
     if (T == 1) gemv_dense(mats, n_mats, hidden, h, DENSE_STORE, nullptr, 1.f, s);
     else for (int m = 0; m < n_mats; m++) rows_matmul(mats[m].y, h, *mat_w[m], T, s);

@@ -118,7 +118,7 @@ def sink_attention(Hx, P, p, m, eps, pos, v_first=None):
     q = rotate_for(norm_plain(q, P[p + "q.norm"], eps), pos, m)
     k = rotate_for(norm_plain(k, P[p + "k.norm"], eps), pos, m)
     if v_first is not None:
-        lam = float(P[p + "vmix"])
+        lam = float(np.asarray(P[p + "vmix"]).reshape(-1)[0])
         v = (1.0 - lam) * v + lam * v_first
     Wt = causal_weights(q, k, m["scale"], H // G, sink=P[p + "sink"])
     return apply_weights(Wt, v, H // G) @ P[p + "o"].T, v
@@ -129,9 +129,10 @@ def talking_attention(Hx, P, p, m, eps, pos):
     positions, per-head temperature, softmax, weights mixed across heads, biased output projection."""
     T = Hx.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = causal_conv(Hx @ P[p + "q"].T + P[p + "q.b"], P[p + "q.conv"]).reshape(T, H, D)
-    k = causal_conv(Hx @ P[p + "k"].T + P[p + "k.b"], P[p + "k.conv"]).reshape(T, G, D)
-    v = causal_conv(Hx @ P[p + "v"].T + P[p + "v.b"], P[p + "v.conv"]).reshape(T, G, V)
+    conv = (lambda u, n: causal_conv(u, P[p + n + ".conv"])) if m.get("conv") else (lambda u, n: u)
+    q = conv(Hx @ P[p + "q"].T + P[p + "q.b"], "q").reshape(T, H, D)
+    k = conv(Hx @ P[p + "k"].T + P[p + "k.b"], "k").reshape(T, G, D)
+    v = conv(Hx @ P[p + "v"].T + P[p + "v.b"], "v").reshape(T, G, V)
     q = rotate_for(norm_plain(q, P[p + "q.norm"], eps), pos, m)
     k = rotate_for(norm_plain(k, P[p + "k.norm"], eps), pos, m)
     Wt = causal_weights(q, k, m["scale"], H // G, temp=P[p + "temp"])
@@ -207,3 +208,126 @@ def forward(cfg, P, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(X.copy())
     return norm_zero_centred(X, P["final.norm"], eps) @ P["head"].T
+
+
+# ---------------------------------------------------------------- random configurations and weights for the tests
+def bf16_grid(a):
+    """Values a bfloat16 holds exactly (round to nearest even), so that 16-bit and 32-bit weight storage describe the same model."""
+    b = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32).astype(np.float64).reshape(np.shape(a))
+
+
+def make_config(pattern=("parallel", "attention", "parallel", "attention"), vocab=53, width=48, ff=40, mlp=None, alpha=1.7, eps=1e-5,
+                left=None, right=None, attn=None, v_mix=(1, 3), left_scale=1.3, right_scale=0.8):
+    """The family's config.json as a dict.  left / right / attn override the mixers' sizes; mlp: per layer True / False; v_mix: the
+    attention layers that blend their values with the first of them."""
+    lf = dict(heads=4, kv_heads=2, dim=12, vdim=10, conv=3, rot_dims=8, base=10000.0, factor=4.0)
+    lf.update(left or {})
+    rt = dict(heads=4, kv_heads=2, dim=10, vdim=6, conv=2, decay_rank=5, gate_rank=7)
+    rt.update(right or {})
+    at = dict(heads=4, kv_heads=2, dim=8, vdim=12, rot_dims=4, base=500.0)
+    at.update(attn or {})
+
+    def rot_of(d, with_factor):
+        if not d["rot_dims"]:
+            return None
+        r = {"base": d["base"], "dims": d["rot_dims"]}
+        if with_factor and d.get("factor"):
+            r["scaling"] = {"factor": d["factor"]}
+        return r
+
+    layers = []
+    for i, typ in enumerate(pattern):
+        if typ == "parallel":
+            L = {"heads": lf["heads"], "kv_heads": lf["kv_heads"], "dim": lf["dim"], "vdim": lf["vdim"], "scale": lf["dim"] ** -0.5}
+            if lf["conv"]:
+                L["conv"] = lf["conv"]
+            if rot_of(lf, True):
+                L["rot"] = rot_of(lf, True)
+            R = {k: rt[k] for k in ("heads", "kv_heads", "dim", "vdim", "conv", "decay_rank", "gate_rank")}
+            m = {"left": L, "right": R, "left_scale": left_scale, "right_scale": right_scale}
+        else:
+            m = {"heads": at["heads"], "kv_heads": at["kv_heads"], "dim": at["dim"], "vdim": at["vdim"], "scale": at["dim"] ** -0.5}
+            if rot_of(at, False):
+                m["rot"] = rot_of(at, False)
+            if i in v_mix:
+                m["v_mix"] = True
+        has_mlp = True if mlp is None else bool(mlp[i % len(mlp)])
+        layers.append({"type": typ, "mixer": m, "mlp": {"kind": "dense", "ff": ff} if has_mlp else None})
+    return {"architecture": "Savidra", "vocab": vocab, "width": width, "norm": {"eps": eps}, "postln_alpha": alpha, "layers": layers}
+
+
+def random_weights(rng, cfg):
+    W = cfg["width"]
+    P = {}
+
+    def mat(rows, cols, gain=1.0):
+        return bf16_grid(rng.standard_normal((rows, cols)) * gain * cols ** -0.5)
+
+    def vec(n, mean=0.0, std=0.2):
+        return bf16_grid(mean + std * rng.standard_normal(n))
+
+    P["embed"] = mat(cfg["vocab"], W, W ** 0.5)
+    P["final.norm"] = vec(W)
+    P["head"] = mat(cfg["vocab"], W)
+    first_mix = None
+    for i, L in enumerate(cfg["layers"]):
+        p = "l%d." % i
+        P[p + "norm1"] = vec(W)
+        P[p + "shift"] = bf16_grid(rng.uniform(0.0, 0.9, W))
+        if L["type"] == "parallel":
+            m = L["mixer"]["left"]
+            q = p + "mix.left."
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * V)):
+                P[q + n] = mat(rows, W, 1.5)
+                P[q + n + ".b"] = vec(rows, 0.0, 0.3)
+                if m.get("conv"):
+                    P[q + n + ".conv"] = bf16_grid(rng.standard_normal((rows, m["conv"])) * 0.6 + 0.2)
+            P[q + "q.norm"] = vec(D, 1.0, 0.3)
+            P[q + "k.norm"] = vec(D, 1.0, 0.3)
+            P[q + "talk"] = bf16_grid(np.eye(H) * 0.7 + rng.standard_normal((H, H)) * 0.3)
+            P[q + "temp"] = bf16_grid(rng.uniform(0.5, 2.0, H))
+            P[q + "o"] = mat(W, H * V)
+            P[q + "o.b"] = vec(W, 0.0, 0.2)
+            m = L["mixer"]["right"]
+            q = p + "mix.right."
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * V)):
+                P[q + n] = mat(rows, W, 1.5)
+                P[q + n + ".conv"] = bf16_grid(rng.standard_normal((rows, m["conv"])) * 0.6 + 0.2)
+            P[q + "b"] = mat(H, W)
+            P[q + "A_log"] = bf16_grid(rng.uniform(-3.0, 0.5, H))
+            P[q + "norm"] = vec(V, 1.0, 0.2)
+            P[q + "a1"] = mat(m["decay_rank"], W)
+            P[q + "a2"] = mat(H * D, m["decay_rank"])
+            P[q + "dt_bias"] = bf16_grid(rng.uniform(-4.0, -1.0, H * D))
+            P[q + "g1"] = mat(m["gate_rank"], W)
+            P[q + "g2"] = mat(H * V, m["gate_rank"], 2.0)
+            P[q + "o"] = mat(W, H * V)
+        else:
+            m = L["mixer"]
+            q = p + "mix."
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            P[q + "q"] = mat(H * D, W, 1.5)
+            P[q + "k"] = mat(G * D, W, 1.5)
+            P[q + "v"] = mat(G * V, W)
+            P[q + "q.norm"] = vec(D, 1.0, 0.3)
+            P[q + "k.norm"] = vec(D, 1.0, 0.3)
+            P[q + "sink"] = bf16_grid(rng.uniform(-1.0, 4.0, H))
+            if m.get("v_mix"):
+                P[q + "vmix"] = bf16_grid(np.array(rng.uniform(0.2, 0.6)))
+            P[q + "o"] = mat(W, H * V)
+        if L.get("mlp"):
+            f = L["mlp"]["ff"]
+            P[p + "norm2"] = vec(W)
+            P[p + "mlp.gate"] = mat(f, W)
+            P[p + "mlp.up"] = mat(f, W)
+            P[p + "mlp.down"] = mat(W, f)
+    return P
+
+
+def random_model(rng, **kw):
+    cfg = make_config(**kw)
+    return cfg, random_weights(rng, cfg)
