@@ -893,6 +893,77 @@ def run_family_compare_tanolorn(args):
                       "dtype": "bf16 weights, f32 activations", "data": "synthetic", "rows": rows}))
 
 
+# width -> (left attention: heads, kv heads, key width, value width), (delta rule: heads, q / k heads, key width, value width, ranks),
+# (sink attention: heads, kv heads, key / value width), and the matching state-space / latent sizes of the family it stands beside
+SAVIDRA_SIZES = {
+    "w2048": dict(width=2048, left=dict(heads=16, kv_heads=2, dim=128, vdim=64), right=dict(heads=16, kv_heads=16, dim=64, vdim=128, decay_rank=64, gate_rank=64),
+                  attn=dict(heads=16, kv_heads=4, dim=128, vdim=128), other=dict(heads=16, dim=64, rot_dim=64, vdim=128, q_rank=768, kv_rank=256, s_heads=32, s_vdim=64, state=64)),
+    "w4096": dict(width=4096, left=dict(heads=32, kv_heads=2, dim=128, vdim=64), right=dict(heads=32, kv_heads=16, dim=128, vdim=128, decay_rank=128, gate_rank=128),
+                  attn=dict(heads=32, kv_heads=8, dim=128, vdim=128), other=dict(heads=32, dim=64, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, s_heads=64, s_vdim=64, state=128)),
+}
+
+
+def run_family_compare_savidra(args):
+    """--family-compare --family savidra: prompt-pass and decode throughput of the Savidra family (BF16 weights; head-mixed attention beside
+    the gated delta rule, sink attention with blended values, token shift, norm on the residual sum, ReLU-gated feed-forward) beside the
+    closest existing family (Tanolorn: post-norm, a recurrent mixer with a short convolution and carried state alternating with rotary
+    attention, dense gated feed-forward) at equal width, layer count and feed-forward width.  Device-timed with CUDA events on the model's
+    stream; prompts differ between steps and the weights of either model exceed L2."""
+    import torch
+    from ntransformer_b200 import kernels as K
+    from ntransformer_b200.engine import Model
+    from ntransformer_b200.model_spec import savidra_config, savidra_random_tensors, tanolorn_config, tanolorn_random_tensors
+
+    torch.cuda.set_device(0)
+    vocab, prompt_len, max_seq = 32000, 2048, 4096
+    hbm, hbm_src = measured_peak_hbm()
+    rows = []
+    for name, z in SAVIDRA_SIZES.items():
+        width, o = z["width"], z["other"]
+        sc = savidra_config(vocab=vocab, width=width, ff=2 * width, left=z["left"], right=z["right"], attn=z["attn"])
+        tc = tanolorn_config(vocab=vocab, width=width, pattern=("mamba2", "latent_attention", "mamba2", "latent_attention"), mlp=("dense",), heads=o["heads"],
+                             dim=o["dim"], rot_dim=o["rot_dim"], vdim=o["vdim"], q_rank=o["q_rank"], kv_rank=o["kv_rank"], s_heads=o["s_heads"], s_vdim=o["s_vdim"],
+                             state=o["state"], groups=8, norm_groups=8, ff=2 * width, side=0)
+        row = {"size": name, "layers": 4, "prompt_tokens": prompt_len, "decode_context": prompt_len}
+        for label, make in (("savidra_bf16", lambda: Model.from_config_json(sc, savidra_random_tensors(sc), max_context=max_seq)),
+                            ("tanolorn_bf16", lambda: Model.from_config_json(tc, tanolorn_random_tensors(tc), max_context=max_seq))):
+            model = make()
+            stream = torch.cuda.ExternalStream(model.stream)
+            prompts = [[token_at(i + 97 * j, vocab) for i in range(prompt_len)] for j in range(4)]
+            for i in range(args.warmup):
+                model.forward_async(prompts[i % 4], 0)
+            model.sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n0 = K.launch_count()
+            psteps = max(3, min(args.steps, 8))
+            a.record(stream)
+            for i in range(psteps):
+                model.forward_async(prompts[i % 4], 0)
+            b.record(stream)
+            model.sync()
+            prefill = psteps * prompt_len / (a.elapsed_time(b) / 1e3)
+            dsteps = max(8, min(args.steps, 256))
+            for i in range(args.warmup):
+                model.forward_async([token_at(i, vocab)], prompt_len + i)
+            model.sync()
+            a.record(stream)
+            for i in range(dsteps):
+                model.forward_async([token_at(i + 5, vocab)], prompt_len + args.warmup + i)
+            b.record(stream)
+            model.sync()
+            ms = a.elapsed_time(b) / dsteps
+            bpt = model.bytes_per_token(prompt_len + args.warmup + dsteps // 2)
+            row[label] = {"prefill_tok_s": round(prefill, 1), "decode_tok_s": round(1e3 / ms, 1), "decode_ms": round(ms, 4),
+                          "decode_bytes_per_token": bpt, "decode_frac_of_hbm_peak": round(bpt / (ms * 1e-3) / (hbm * 1e9), 3),
+                          "launches": int(K.launch_count() - n0)}
+            model.close()
+            del model
+            torch.cuda.empty_cache()
+        rows.append(row)
+    print(json.dumps({"metric": "family_compare", "family": "savidra", "unit": "tok/s", "hbm_peak_gbs": hbm, "hbm_peak_source": hbm_src,
+                      "dtype": "bf16 weights, f32 activations", "data": "synthetic", "rows": rows}))
+
+
 def run_family_compare(args):
     """--family-compare: prompt-pass and decode throughput of the Zelunex family (BF16 weights, windowed attention) beside the
     closest GGUF family member (Llama block, F16 weights, full causal attention) at equal layer sizes.  Device-timed with CUDA
@@ -969,8 +1040,8 @@ def main():
     ap.add_argument("--all-errs", action="store_true", help="--check only: list the error of every step, not the first 8")
     ap.add_argument("--family-compare", action="store_true",
                     help="instead of the workload: Zelunex beside the Llama block at equal layer sizes, prompt pass and decode (1 GPU)")
-    ap.add_argument("--family", default="zelunex", choices=["zelunex", "vebotar", "tanolorn"],
-                    help="--family-compare only: zelunex beside the Llama block (default), vebotar beside zelunex, or tanolorn beside vebotar")
+    ap.add_argument("--family", default="zelunex", choices=["zelunex", "vebotar", "tanolorn", "savidra"],
+                    help="--family-compare only: zelunex beside the Llama block (default), vebotar beside zelunex, tanolorn beside vebotar, or savidra beside tanolorn")
     ap.add_argument("--per-token-prompt", action="store_true", help="--check only: our engine replays the prompt token by token like the reference")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -980,7 +1051,7 @@ def main():
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     if args.family_compare:
         if rank == 0:
-            {"vebotar": run_family_compare_vebotar, "tanolorn": run_family_compare_tanolorn}.get(args.family, run_family_compare)(args)
+            {"vebotar": run_family_compare_vebotar, "tanolorn": run_family_compare_tanolorn, "savidra": run_family_compare_savidra}.get(args.family, run_family_compare)(args)
     elif args.check:
         run_check(args, rank, world)
     elif args.impl == "reference":

@@ -316,3 +316,105 @@ def tanolorn_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype
             t[p + "side.proj"] = mat(W, side)
             t[p + "side.norm"] = vec(W, 1.0)
     return t
+
+
+# ---- Savidra (layer-spec family, model folders): synthetic configurations and random device weights for benchmarks ----
+def savidra_config(vocab=32000, width=2048, pattern=("parallel", "attention", "parallel", "attention"), ff=4096, v_mix=(1, 3), alpha=2.0, eps=1e-6,
+                   left=None, right=None, attn=None, left_scale=1.0, right_scale=1.0):
+    """The family's config.json as a dict.  pattern: mixer type per layer ("parallel": head-mixed attention beside the gated delta rule;
+    "attention": sink attention); left / right / attn override the mixers' sizes; v_mix: the attention layers whose values blend with the
+    first of them; ff: feed-forward width (0: none)."""
+    lf = dict(heads=16, kv_heads=2, dim=128, vdim=64, conv=4, rot_dims=128, base=1e6, factor=8.0)
+    lf.update(left or {})
+    rt = dict(heads=16, kv_heads=16, dim=64, vdim=128, conv=4, decay_rank=64, gate_rank=64)
+    rt.update(right or {})
+    at = dict(heads=16, kv_heads=4, dim=128, vdim=128, rot_dims=64, base=1e6)
+    at.update(attn or {})
+    layers = []
+    for i, typ in enumerate(pattern):
+        if typ == "parallel":
+            L = {"heads": lf["heads"], "kv_heads": lf["kv_heads"], "dim": lf["dim"], "vdim": lf["vdim"], "scale": lf["dim"] ** -0.5, "conv": lf["conv"],
+                 "rot": {"base": lf["base"], "dims": lf["rot_dims"], "scaling": {"factor": lf["factor"]}}}
+            m = {"left": L, "right": dict(rt), "left_scale": left_scale, "right_scale": right_scale}
+        else:
+            m = {"heads": at["heads"], "kv_heads": at["kv_heads"], "dim": at["dim"], "vdim": at["vdim"], "scale": at["dim"] ** -0.5,
+                 "rot": {"base": at["base"], "dims": at["rot_dims"]}}
+            if i in v_mix:
+                m["v_mix"] = True
+        layers.append({"type": typ, "mixer": m, "mlp": {"kind": "dense", "ff": ff} if ff else None})
+    return {"architecture": "Savidra", "vocab": vocab, "width": width, "norm": {"eps": eps}, "postln_alpha": alpha, "layers": layers}
+
+
+def savidra_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype=None):
+    """Checkpoint name -> random CUDA tensor (matrices `dtype`, default bfloat16; gains, biases, convolution taps, head tables and the
+    delta rule's constants float32)."""
+    import torch
+
+    dtype = dtype or torch.bfloat16
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W = config["width"]
+
+    def mat(rows, cols, dt=dtype):
+        return (torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32) * cols ** -0.5).to(dt)
+
+    def vec(n, mean=0.0, std=0.1):
+        return mean + std * torch.randn(n, generator=g, device=device, dtype=torch.float32)
+
+    def uni(n, lo, hi):
+        return lo + (hi - lo) * torch.rand(n, generator=g, device=device, dtype=torch.float32)
+
+    def taps(rows, n):
+        return 0.2 + 0.5 * torch.randn(rows, n, generator=g, device=device, dtype=torch.float32)
+
+    t = {"embed": mat(config["vocab"], W) * W ** 0.5, "final.norm": vec(W), "head": mat(config["vocab"], W)}
+    for i, e in enumerate(config["layers"]):
+        p = "l%d." % i
+        t[p + "norm1"] = vec(W)
+        t[p + "shift"] = uni(W, 0.0, 0.8)
+        if e["type"] == "parallel":
+            m, q = e["mixer"]["left"], p + "mix.left."
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * V)):
+                t[q + n] = mat(rows, W)
+                t[q + n + ".b"] = vec(rows)
+                t[q + n + ".conv"] = taps(rows, m["conv"])
+            t[q + "q.norm"] = vec(D, 1.0)
+            t[q + "k.norm"] = vec(D, 1.0)
+            t[q + "talk"] = torch.eye(H, device=device) * 0.7 + 0.2 * torch.randn(H, H, generator=g, device=device)
+            t[q + "temp"] = uni(H, 0.6, 1.8)
+            t[q + "o"] = mat(W, H * V)
+            t[q + "o.b"] = vec(W)
+            m, q = e["mixer"]["right"], p + "mix.right."
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * V)):
+                t[q + n] = mat(rows, W)
+                t[q + n + ".conv"] = taps(rows, m["conv"])
+            t[q + "b"] = mat(H, W)
+            t[q + "A_log"] = uni(H, -3.0, 0.3)
+            t[q + "norm"] = vec(V, 1.0)
+            t[q + "a1"] = mat(m["decay_rank"], W)
+            t[q + "a2"] = mat(H * D, m["decay_rank"])
+            t[q + "dt_bias"] = uni(H * D, -4.0, -1.0)
+            t[q + "g1"] = mat(m["gate_rank"], W)
+            t[q + "g2"] = mat(H * V, m["gate_rank"])
+            t[q + "o"] = mat(W, H * V)
+        else:
+            m, q = e["mixer"], p + "mix."
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            t[q + "q"] = mat(H * D, W)
+            t[q + "k"] = mat(G * D, W)
+            t[q + "v"] = mat(G * V, W)
+            t[q + "q.norm"] = vec(D, 1.0)
+            t[q + "k.norm"] = vec(D, 1.0)
+            t[q + "sink"] = uni(H, 0.0, 4.0)
+            if m.get("v_mix"):
+                t[q + "vmix"] = uni(1, 0.2, 0.6)
+            t[q + "o"] = mat(W, H * V)
+        f = e.get("mlp")
+        if f:
+            t[p + "norm2"] = vec(W)
+            t[p + "mlp.gate"] = mat(f["ff"], W)
+            t[p + "mlp.up"] = mat(f["ff"], W)
+            t[p + "mlp.down"] = mat(W, f["ff"])
+    return t
