@@ -7,8 +7,9 @@
 //   delta_rule_rows   the recurrence.  Every column j of S (the dim numbers that produce value channel j) evolves on its own:
 //                         s <- a * s;  d1 = <k, s>;  d2 = <q, s>;  u = beta (v_j - d1);  s <- s + k u;  o_j = d2 + <q, k> u,
 //                     so one reduction per token serves both the correction and the read-out.  LN lanes share a column (dim / LN state
-//                     numbers each, in registers); a CTA owns 128 / LN columns of one head and walks the step's rows in tiles staged
-//                     through shared memory (q, k, a of the head, v and beta of its columns).  The state [heads, vdim, dim] is read at the
+//                     numbers each, in registers; LN is 2 to 16: the reduction over them is on the dependent chain); a CTA owns its
+//                     threads / LN columns of one head and walks the step's rows in tiles of 16 staged through shared memory by cp.async
+//                     into two buffers (q, k, a of the head, v and beta of its columns).  The state [heads, vdim, dim] is read at the
 //                     start (zeros when the step starts at position 0) and written back at the end, so a prompt cut anywhere — and a
 //                     decoded token, T = 1 — continues exactly.
 //   delta_gate_norm   out = o / sqrt(mean_v(o^2) + eps) * gain[v] * sigmoid(gate_raw), per head
@@ -17,6 +18,7 @@
 #include "kernels_internal.h"
 #include "ring.cuh"
 #include <algorithm>
+#include <cstdint>
 
 namespace nt { namespace b200 {
 
@@ -60,22 +62,25 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(float* __restrict__ q, 
     for (int h = threadIdx.x; h < heads; h += 256) beta[t * heads + h] = sigmoid_f(beta[t * heads + h]);
 }
 
-constexpr int DR_THREADS = 128;
 constexpr int DR_TILE = 16;      // rows staged per tile
 
-// grid (ceil(vdim / (128 / LN)), heads).  Lane l of a column holds state elements l + LN * e, e < NPT.
-template <int LN, int NPT>
-__global__ void __launch_bounds__(DR_THREADS) delta_rule_rows_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
-                                                                    const float* __restrict__ v, const float* __restrict__ a, const float* __restrict__ beta,
-                                                                    const float* __restrict__ qk, float* __restrict__ state, int T, int heads, int kv_heads,
-                                                                    int dim, int vdim, const int* __restrict__ pos_dev, int p0) {
-    constexpr int COLS = DR_THREADS / LN;
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// grid (ceil(vdim / (THREADS / LN)), heads).  Lane l of a column holds state elements l + LN * e, e < NPT.  Two tile buffers: the next
+// tile's rows arrive (cp.async) while the current one is walked.
+template <int LN, int NPT, int THREADS>
+__global__ void __launch_bounds__(THREADS) delta_rule_rows_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
+                                                                 const float* __restrict__ v, const float* __restrict__ a, const float* __restrict__ beta,
+                                                                 const float* __restrict__ qk, float* __restrict__ state, int T, int heads, int kv_heads,
+                                                                 int dim, int vdim, const int* __restrict__ pos_dev, int p0) {
+    constexpr int COLS = THREADS / LN;
     extern __shared__ __align__(16) float sm[];
-    float* sq = sm;                           // [DR_TILE][dim]
-    float* sk = sq + DR_TILE * dim;
-    float* sa = sk + DR_TILE * dim;
-    float* sv = sa + DR_TILE * dim;           // [DR_TILE][COLS]
-    float* sb = sv + DR_TILE * COLS;          // [DR_TILE] beta, [DR_TILE] <q, k>
+    const int tile_floats = 3 * DR_TILE * dim + DR_TILE * COLS + 2 * DR_TILE;     // q | k | a [DR_TILE][dim], v [DR_TILE][COLS], beta, <q, k> [DR_TILE]
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y, g = h / (heads / kv_heads);
@@ -87,39 +92,63 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_rows_kernel(float* __re
     float S[NPT];
 #pragma unroll
     for (int e = 0; e < NPT; e++) { const int d = l + LN * e; S[e] = (live && !fresh && d < dim) ? st[d] : 0.f; }
-    for (int t0 = 0; t0 < T; t0 += DR_TILE) {
+    auto load_tile = [&](int t0, int buf) {
+        float* sq = sm + (size_t)buf * tile_floats;
+        float* sk = sq + DR_TILE * dim;
+        float* sa = sk + DR_TILE * dim;
+        float* sv = sa + DR_TILE * dim;
+        float* sb = sv + DR_TILE * COLS;
         const int nt = min(DR_TILE, T - t0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * dim; i += DR_THREADS) {
+        for (int i = threadIdx.x; i < nt * dim; i += THREADS) {
             const int tt = i / dim, d = i % dim;
             const size_t t = (size_t)(t0 + tt);
-            sq[i] = q[(t * kv_heads + g) * dim + d];
-            sk[i] = k[(t * kv_heads + g) * dim + d];
-            sa[i] = a[(t * heads + h) * dim + d];
+            cp_async4(sq + i, q + (t * kv_heads + g) * dim + d);
+            cp_async4(sk + i, k + (t * kv_heads + g) * dim + d);
+            cp_async4(sa + i, a + (t * heads + h) * dim + d);
         }
-        for (int i = threadIdx.x; i < nt * COLS; i += DR_THREADS) {
+        for (int i = threadIdx.x; i < nt * COLS; i += THREADS) {
             const int tt = i / COLS, c = blockIdx.x * COLS + i % COLS;
-            sv[i] = c < vdim ? v[((size_t)(t0 + tt) * heads + h) * vdim + c] : 0.f;
+            if (c < vdim) cp_async4(sv + i, v + ((size_t)(t0 + tt) * heads + h) * vdim + c);
+            else sv[i] = 0.f;
         }
-        for (int i = threadIdx.x; i < nt; i += DR_THREADS) {
-            sb[i] = beta[(size_t)(t0 + i) * heads + h];
-            sb[DR_TILE + i] = qk[(size_t)(t0 + i) * kv_heads + g];
+        for (int i = threadIdx.x; i < nt; i += THREADS) {
+            cp_async4(sb + i, beta + (size_t)(t0 + i) * heads + h);
+            cp_async4(sb + DR_TILE + i, qk + (size_t)(t0 + i) * kv_heads + g);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = (T + DR_TILE - 1) / DR_TILE;
+    load_tile(0, 0);
+    for (int j = 0; j < n_tiles; j++) {
+        const int t0 = j * DR_TILE, nt = min(DR_TILE, T - t0), buf = j & 1;
+        if (j + 1 < n_tiles) {
+            load_tile(t0 + DR_TILE, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const float* sq = sm + (size_t)buf * tile_floats;
+        const float* sk = sq + DR_TILE * dim;
+        const float* sa = sk + DR_TILE * dim;
+        const float* sv = sa + DR_TILE * dim;
+        const float* sb = sv + DR_TILE * COLS;
         for (int tt = 0; tt < nt; tt++) {
             const float* kq = sk + tt * dim;
             const float* qq = sq + tt * dim;
             const float* aa = sa + tt * dim;
-            float d1 = 0.f, d2 = 0.f;
+            // two partial sums per dot product: half the dependent chain
+            float d1a = 0.f, d1b = 0.f, d2a = 0.f, d2b = 0.f;
 #pragma unroll
             for (int e = 0; e < NPT; e++) {
                 const int d = l + LN * e;
                 if (d < dim) {
                     S[e] *= aa[d];
-                    d1 = fmaf(kq[d], S[e], d1);
-                    d2 = fmaf(qq[d], S[e], d2);
+                    if (e & 1) { d1b = fmaf(kq[d], S[e], d1b); d2b = fmaf(qq[d], S[e], d2b); }
+                    else { d1a = fmaf(kq[d], S[e], d1a); d2a = fmaf(qq[d], S[e], d2a); }
                 }
             }
+            float d1 = d1a + d1b, d2 = d2a + d2b;
 #pragma unroll
             for (int o = LN / 2; o > 0; o >>= 1) { d1 += __shfl_xor_sync(0xFFFFFFFFu, d1, o); d2 += __shfl_xor_sync(0xFFFFFFFFu, d2, o); }
             const float u = sb[tt] * (sv[tt * COLS + col_l] - d1);
@@ -127,10 +156,113 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_rows_kernel(float* __re
             for (int e = 0; e < NPT; e++) { const int d = l + LN * e; if (d < dim) S[e] = fmaf(kq[d], u, S[e]); }
             if (l == 0 && live) out[((size_t)(t0 + tt) * heads + h) * vdim + col] = fmaf(sb[DR_TILE + tt], u, d2);
         }
+        __syncthreads();                       // the buffer is refilled by the load of tile j + 2
     }
     if (live) {
 #pragma unroll
         for (int e = 0; e < NPT; e++) { const int d = l + LN * e; if (d < dim) st[d] = S[e]; }
+    }
+}
+
+// The same recurrence for key widths that are a multiple of 4: lane l of a column holds CH chunks of 4 consecutive state numbers
+// (chunk c at d = 4 (c LN + l)), so q, k, a come from shared memory as 16-byte loads and the per-row instruction count drops to a
+// third; LN is chosen as wide as the head allows (dim / 4 lanes), which keeps more warps in flight — the kernel issues one instruction
+// every three to four cycles per warp, so warps per scheduler, not work per lane, set its speed.
+template <int LN, int CH>
+__global__ void __launch_bounds__(128) delta_rule_rows_vec_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
+                                                                 const float* __restrict__ v, const float* __restrict__ a, const float* __restrict__ beta,
+                                                                 const float* __restrict__ qk, float* __restrict__ state, int T, int heads, int kv_heads,
+                                                                 int dim, int vdim, const int* __restrict__ pos_dev, int p0) {
+    constexpr int THREADS = 128, COLS = THREADS / LN;
+    extern __shared__ __align__(16) float sm[];
+    const int tile_floats = 3 * DR_TILE * dim + DR_TILE * COLS + 2 * DR_TILE;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, g = h / (heads / kv_heads);
+    const int col_l = threadIdx.x / LN, l = threadIdx.x % LN;
+    const int col = blockIdx.x * COLS + col_l;
+    const bool live = col < vdim;
+    const bool fresh = (pos_dev ? *pos_dev : p0) == 0;
+    float* st = state + ((size_t)h * vdim + (live ? col : 0)) * dim;
+    int d0[CH];
+    bool on[CH];
+    float4 S[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+        d0[c] = 4 * (c * LN + l);
+        on[c] = d0[c] < dim;
+        S[c] = (on[c] && live && !fresh) ? *reinterpret_cast<const float4*>(st + d0[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!on[c]) d0[c] = 0;                  // an idle chunk reads a valid address and keeps zeros
+    }
+    auto load_tile = [&](int t0, int buf) {
+        float* sq = sm + (size_t)buf * tile_floats;
+        float* sk = sq + DR_TILE * dim;
+        float* sa = sk + DR_TILE * dim;
+        float* sv = sa + DR_TILE * dim;
+        float* sb = sv + DR_TILE * COLS;
+        const int nt = min(DR_TILE, T - t0), d4 = dim / 4;
+        for (int i = threadIdx.x; i < nt * d4; i += THREADS) {
+            const int tt = i / d4, d = (i % d4) * 4;
+            const size_t t = (size_t)(t0 + tt);
+            cp_async16(sq + tt * dim + d, q + (t * kv_heads + g) * dim + d);
+            cp_async16(sk + tt * dim + d, k + (t * kv_heads + g) * dim + d);
+            cp_async16(sa + tt * dim + d, a + (t * heads + h) * dim + d);
+        }
+        for (int i = threadIdx.x; i < nt * COLS; i += THREADS) {
+            const int tt = i / COLS, c = blockIdx.x * COLS + i % COLS;
+            if (c < vdim) cp_async4(sv + i, v + ((size_t)(t0 + tt) * heads + h) * vdim + c);
+            else sv[i] = 0.f;
+        }
+        for (int i = threadIdx.x; i < nt; i += THREADS) {
+            cp_async4(sb + i, beta + (size_t)(t0 + i) * heads + h);
+            cp_async4(sb + DR_TILE + i, qk + (size_t)(t0 + i) * kv_heads + g);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = (T + DR_TILE - 1) / DR_TILE;
+    load_tile(0, 0);
+    for (int j = 0; j < n_tiles; j++) {
+        const int t0 = j * DR_TILE, nt = min(DR_TILE, T - t0), buf = j & 1;
+        if (j + 1 < n_tiles) {
+            load_tile(t0 + DR_TILE, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* sq = sm + (size_t)buf * tile_floats;
+        const float* sk = sq + DR_TILE * dim;
+        const float* sa = sk + DR_TILE * dim;
+        const float* sv = sa + DR_TILE * dim;
+        const float* sb = sv + DR_TILE * COLS;
+        for (int tt = 0; tt < nt; tt++) {
+            float4 kk[CH];
+            float d1 = 0.f, d2 = 0.f;
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                const float4 aa = *reinterpret_cast<const float4*>(sa + tt * dim + d0[c]);
+                const float4 qq = *reinterpret_cast<const float4*>(sq + tt * dim + d0[c]);
+                kk[c] = *reinterpret_cast<const float4*>(sk + tt * dim + d0[c]);
+                S[c].x *= aa.x; S[c].y *= aa.y; S[c].z *= aa.z; S[c].w *= aa.w;
+                d1 = fmaf(kk[c].x, S[c].x, d1); d2 = fmaf(qq.x, S[c].x, d2);
+                d1 = fmaf(kk[c].y, S[c].y, d1); d2 = fmaf(qq.y, S[c].y, d2);
+                d1 = fmaf(kk[c].z, S[c].z, d1); d2 = fmaf(qq.z, S[c].z, d2);
+                d1 = fmaf(kk[c].w, S[c].w, d1); d2 = fmaf(qq.w, S[c].w, d2);
+            }
+#pragma unroll
+            for (int o = LN / 2; o > 0; o >>= 1) { d1 += __shfl_xor_sync(0xFFFFFFFFu, d1, o); d2 += __shfl_xor_sync(0xFFFFFFFFu, d2, o); }
+            const float u = sb[tt] * (sv[tt * COLS + col_l] - d1);
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                if (on[c]) { S[c].x = fmaf(kk[c].x, u, S[c].x); S[c].y = fmaf(kk[c].y, u, S[c].y); S[c].z = fmaf(kk[c].z, u, S[c].z); S[c].w = fmaf(kk[c].w, u, S[c].w); }
+            }
+            if (l == 0 && live) out[((size_t)(t0 + tt) * heads + h) * vdim + col] = fmaf(sb[DR_TILE + tt], u, d2);
+        }
+        __syncthreads();
+    }
+    if (live) {
+#pragma unroll
+        for (int c = 0; c < CH; c++) if (on[c]) *reinterpret_cast<float4*>(st + 4 * (c * LN + l)) = S[c];
     }
 }
 
@@ -151,15 +283,26 @@ __global__ void __launch_bounds__(128) delta_gate_norm_kernel(float* __restrict_
     for (int i = threadIdx.x; i < vdim; i += 128) out[base + i] = o[base + i] * inv * gain[i] * sigmoid_f(gate_raw[base + i]);
 }
 
-template <int LN, int NPT>
+template <int LN, int NPT, int THREADS>
 void launch_rows(float* out, const float* q, const float* k, const float* v, const float* a, const float* beta, const float* qk, float* state, int T, int heads,
                  int kv_heads, int dim, int vdim, const int* pos_dev, int p0, cudaStream_t s) {
-    constexpr int COLS = DR_THREADS / LN;
-    const size_t smem = sizeof(float) * ((size_t)3 * DR_TILE * dim + (size_t)DR_TILE * COLS + 2 * DR_TILE);
+    constexpr int COLS = THREADS / LN;
+    const size_t smem = sizeof(float) * 2 * ((size_t)3 * DR_TILE * dim + (size_t)DR_TILE * COLS + 2 * DR_TILE);
     static unsigned long long done = 0;
-    if (smem > 48 * 1024) opt_in_dynamic_smem(delta_rule_rows_kernel<LN, NPT>, (int)smem, done);
-    launch_k(delta_rule_rows_kernel<LN, NPT>, dim3((vdim + COLS - 1) / COLS, heads), dim3(DR_THREADS), smem, s, out, q, k, v, a, beta, qk, state, T, heads,
+    if (smem > 48 * 1024) opt_in_dynamic_smem(delta_rule_rows_kernel<LN, NPT, THREADS>, (int)smem, done);
+    launch_k(delta_rule_rows_kernel<LN, NPT, THREADS>, dim3((vdim + COLS - 1) / COLS, heads), dim3(THREADS), smem, s, out, q, k, v, a, beta, qk, state, T, heads,
              kv_heads, dim, vdim, pos_dev, p0);
+}
+
+template <int LN, int CH>
+void launch_rows_vec(float* out, const float* q, const float* k, const float* v, const float* a, const float* beta, const float* qk, float* state, int T, int heads,
+                     int kv_heads, int dim, int vdim, const int* pos_dev, int p0, cudaStream_t s) {
+    constexpr int COLS = 128 / LN;
+    const size_t smem = sizeof(float) * 2 * ((size_t)3 * DR_TILE * dim + (size_t)DR_TILE * COLS + 2 * DR_TILE);
+    static unsigned long long done = 0;
+    if (smem > 48 * 1024) opt_in_dynamic_smem(delta_rule_rows_vec_kernel<LN, CH>, (int)smem, done);
+    launch_k(delta_rule_rows_vec_kernel<LN, CH>, dim3((vdim + COLS - 1) / COLS, heads), dim3(128), smem, s, out, q, k, v, a, beta, qk, state, T, heads, kv_heads, dim,
+             vdim, pos_dev, p0);
 }
 
 }  // namespace
@@ -176,12 +319,29 @@ void delta_rule_rows(float* out, const float* q, const float* k, const float* v,
     NT_CHECK(dim >= 1 && dim <= DELTA_MAX_DIM, "delta_rule_rows: key heads wider than 256 are not covered");
     NT_CHECK(kv_heads > 0 && heads % kv_heads == 0, "delta_rule_rows: heads must be a multiple of kv_heads");
     if (T <= 0) return;
-#define NT_DR(LN, NPT) launch_rows<LN, NPT>(out, q, k, v, a, beta, qk, state, T, heads, kv_heads, dim, vdim, pos_dev, p0, s)
-    if (dim <= 16) NT_DR(4, 4);
-    else if (dim <= 32) NT_DR(8, 4);
-    else if (dim <= 64) NT_DR(16, 4);
-    else if (dim <= 128) NT_DR(32, 4);
-    else NT_DR(32, 8);
+    const bool aligned = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(a) |
+                                           reinterpret_cast<uintptr_t>(state)) & 15) == 0;
+    if (aligned) {                  // 16-byte rows: the vector form, dim / 4 lanes per column
+#define NT_DV(LN, CH) launch_rows_vec<LN, CH>(out, q, k, v, a, beta, qk, state, T, heads, kv_heads, dim, vdim, pos_dev, p0, s)
+        if (dim <= 8) NT_DV(2, 1);
+        else if (dim <= 16) NT_DV(4, 1);
+        else if (dim <= 32) NT_DV(8, 1);
+        else if (dim <= 64) NT_DV(16, 1);
+        else if (dim <= 128) NT_DV(32, 1);
+        else NT_DV(32, 2);
+#undef NT_DV
+        count_launch();
+        return;
+    }
+    // few lanes per column keep the per-row reduction short (it sits on the recurrence's dependent chain); CTAs of 64 threads when
+    // CTAs of 128 would leave most SMs without one
+#define NT_DR(LN, NPT) do { if ((long)((vdim + 128 / LN - 1) / (128 / LN)) * heads >= 148) launch_rows<LN, NPT, 128>(out, q, k, v, a, beta, qk, state, T, heads, kv_heads, dim, vdim, pos_dev, p0, s); \
+                            else launch_rows<LN, NPT, 64>(out, q, k, v, a, beta, qk, state, T, heads, kv_heads, dim, vdim, pos_dev, p0, s); } while (0)
+    if (dim <= 16) NT_DR(2, 8);
+    else if (dim <= 32) NT_DR(4, 8);
+    else if (dim <= 64) NT_DR(4, 16);
+    else if (dim <= 128) NT_DR(8, 16);
+    else NT_DR(16, 16);
 #undef NT_DR
     count_launch();
 }

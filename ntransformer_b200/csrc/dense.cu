@@ -228,6 +228,10 @@ __global__ void scaled_add_rows_kernel(float* __restrict__ x, const float* __res
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] = fmaf(alpha * (row_scale ? row_scale[i % cols] : 1.f), y[i], x[i]);
 }
+__global__ void copy_cols_kernel(float* __restrict__ out, const float* __restrict__ in, size_t n, int cols, int ld) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[(i / cols) * ld + i % cols];
+}
 template <typename T>
 __global__ void to_f32_kernel(float* __restrict__ out, const T* __restrict__ in, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -291,6 +295,14 @@ void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pi
 void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s, bool relu) {
     if (!n) return;
     glu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out, gate, up, n, relu ? 2 : (gelu ? 1 : 0));
+    NT_LAUNCH_CHECK();
+    count_launch();
+}
+
+void copy_cols(float* out, const float* in, int rows, int cols, int ld, cudaStream_t s) {
+    const size_t n = (size_t)rows * cols;
+    if (!n) return;
+    copy_cols_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out, in, n, cols, ld);
     NT_LAUNCH_CHECK();
     count_launch();
 }

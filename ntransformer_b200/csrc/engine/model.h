@@ -28,6 +28,10 @@ struct Weight {
     int rows = 0, cols = 0;      // shard shape (out_features, in_features)
     size_t pitch = 0;            // bytes between rows
     bool owned = false;
+    // Layer-spec families: a copy of a short matrix (fewer rows than a tensor-core tile) with zero rows appended up to tc_rows, so that
+    // prompt rows can take the tensor-core GEMM; the first `rows` columns of its result are the product.  Null: none.
+    const void* tc_ptr = nullptr;
+    int tc_rows = 0;
     size_t bytes() const { return (size_t)rows * dtype_row_size(dtype, (size_t)cols); }   // algorithmic bytes
 };
 
@@ -174,7 +178,8 @@ private:
     const LayerSpec& slot_spec(int slot) const { return *slot_spec_[(size_t)slot]; }
     std::vector<const LayerSpec*> slot_spec_;   // the mixer behind every entry of kcs_ / vcs_: the layers first, then the branches that keep rows
     void layer_postnorm(int i, int T, const int* tok_dev, const int* pos_dev, int p0, const RowBufs& B, cudaStream_t s);
-    void rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s);      // C = A . W^T: GEMV for one row, else spec_gemm
+    void rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s, bool* split_done = nullptr);      // C = A . W^T: GEMV for one row, else spec_gemm
+    void pad_for_tensor_cores(Weight& w);     // gives a short BF16 matrix its zero-padded copy (Weight::tc_ptr)
     size_t row_scratch_width() const;         // widest intermediate row of any POST_NORM layer
     void cache_row_widths(int i, size_t& k, size_t& v) const;   // elements per position in layer i's two caches
     int n_streams() const { return cfg_.streams > 0 ? cfg_.streams : 1; }

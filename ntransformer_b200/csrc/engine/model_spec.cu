@@ -775,16 +775,44 @@ size_t Model::row_scratch_width() const {
     return m;
 }
 
+// Short BF16 matrices (rows below a tensor-core tile, cols a multiple of 64) get a copy with zero rows up to 128: the CUDA-core GEMM has
+// one CTA per 64 x 64 outputs and leaves most SMs idle on them.  The copy must not alias the prompt pass's result row buffer: the padded
+// product lands in pf_.tmp, which no caller of rows_matmul passes as A together with such a matrix.
+void Model::pad_for_tensor_cores(Weight& w) {
+    static const bool off = getenv("NT_B200_NO_TC_PREFILL") != nullptr;
+    constexpr int kRows = 128;
+    if (off || exact32_ || !w.ptr || w.dtype != DType::BF16 || w.rows >= kRows || w.cols % 64 != 0 || cfg_.hidden_size < kRows) return;
+    uint8_t* p = dmalloc<uint8_t>((size_t)kRows * w.cols * 2);
+    NT_CUDA_CHECK(cudaMemset(p, 0, (size_t)kRows * w.cols * 2));
+    NT_CUDA_CHECK(cudaMemcpy2D(p, (size_t)w.cols * 2, w.ptr, w.pitch, (size_t)w.cols * 2, (size_t)w.rows, cudaMemcpyDeviceToDevice));
+    if (!gemm_f16_tc_ragged_supported(p, kRows, w.cols, (size_t)w.cols * 2)) { cudaFree(p); return; }
+    owned_.push_back(p);
+    w.tc_ptr = p; w.tc_rows = kRows;
+}
+
 // C [T, w.rows] = A [T, w.cols] . W^T.  One row: the GEMV.  More: the tensor-core GEMM from a BF16 split of A made here when the matrix
 // qualifies (never in exact mode), else the FP32 GEMM on CUDA cores.
-void Model::rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s) {
+void Model::rows_matmul(float* C, const float* A, const Weight& w, int T, cudaStream_t s, bool* split_done) {
     if (T == 1) {
         GemvMat m = mat_of(w, C);
         gemv_dense(&m, 1, w.cols, A, DENSE_STORE, nullptr, 1.f, s);
         return;
     }
+    // split_done: several matrices read the same A one after the other; the first tensor-core one splits it, the others find it done
+    auto split_once = [&]() {
+        if (split_done && *split_done) return;
+        split_activations(pf_.ws, A, T, w.cols, s, true);
+        if (split_done) *split_done = true;
+    };
+    if (w.tc_ptr && pf_.ws && !exact32_) {            // a short matrix: the padded copy on the tensor cores, then the live columns
+        split_once();
+        TcOpts o; o.bf16 = true;
+        NT_CHECK(gemm_f16_tc_ws(pf_.tmp, pf_.ws, w.tc_ptr, T, w.tc_rows, w.cols, false, s, o), "prefill GEMM (padded) rejected");
+        copy_cols(C, pf_.tmp, T, w.rows, w.tc_rows, s);
+        return;
+    }
     const bool tc = pf_.ws && spec_tc_ok(w);
-    if (tc) split_activations(pf_.ws, A, T, w.cols, s, true);
+    if (tc) split_once();
     spec_gemm(C, A, tc ? pf_.ws : nullptr, w, T, DENSE_STORE, nullptr, 1.f, s);
 }
 

@@ -79,6 +79,7 @@ bool Model::finalize_mixer_state(LayerSpec& S, LayerWeights& M, int layer) {
         M.v_conv_state = dmalloc0<float>((size_t)(S.conv - 1) * vw);
     }
     if (delta) M.delta_state = dmalloc0<float>((size_t)S.heads * S.vdim * S.dim);
+    for (Weight* w : {&M.wq, &M.wk, &M.wv, &M.d_beta, &M.d_a1, &M.d_g1}) pad_for_tensor_cores(*w);
     if (!delta && S.rot.dims > 0) {
         const RotarySpec& R = S.rot;
         std::vector<float> f((size_t)R.dims / 2);
@@ -215,7 +216,10 @@ void Model::layer_sumnorm(int i, int T, const int* pos_dev, int p0, const RowBuf
     NT_CHECK(off <= sumnorm_scratch_width() && cur <= sumnorm_scratch_width() * (size_t)T, "layer_sumnorm: scratch rows overrun");
     // ---- projections (one launch for a decoded token), convolutions (one launch), then each mixer ----
     if (T == 1) gemv_dense(mats, n_mats, hidden, h, DENSE_STORE, nullptr, 1.f, s);
-    else for (int m = 0; m < n_mats; m++) rows_matmul(mats[m].y, h, *mat_w[m], T, s);
+    else {
+        bool split_done = false;                       // every projection reads h: its 16-bit split is made once
+        for (int m = 0; m < n_mats; m++) rows_matmul(mats[m].y, h, *mat_w[m], T, s, &split_done);
+    }
     if (n_segs > 0) short_conv(segs, n_segs, T, pos_dev, p0, s);
     for (int m = 0; m < n_mix; m++) {
         float* y = m == 0 ? y1 : y2;
@@ -235,8 +239,9 @@ void Model::layer_sumnorm(int i, int T, const int* pos_dev, int p0, const RowBuf
             GemvMat gu[2] = {mat_of(L.gate, g), mat_of(L.up, nullptr)};
             gemv_dense(gu, 2, hidden, B.x, S.act == GluAct::RELU ? DENSE_REGLU : (S.act == GluAct::GELU_TANH ? DENSE_GEGLU : DENSE_SWIGLU), nullptr, 1.f, s);
         } else {
-            rows_matmul(g, B.x, L.gate, T, s);
-            rows_matmul(up, B.x, L.up, T, s);
+            bool split_done = false;
+            rows_matmul(g, B.x, L.gate, T, s, &split_done);
+            rows_matmul(up, B.x, L.up, T, s, &split_done);
             glu_mul(g, g, up, (size_t)T * S.ff, S.act == GluAct::GELU_TANH, s, S.act == GluAct::RELU);
         }
         rows_matmul(B.y, g, L.down, T, s);

@@ -152,6 +152,7 @@ void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pi
 void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s, bool relu = false);      // out = act(gate) * up (SiLU, tanh-GELU or ReLU)
 void scaled_add_rows(float* x, const float* y, const float* row_scale, float alpha, int rows, int cols, cudaStream_t s);   // x[r,c] += alpha * row_scale[c] * y[r,c]
 void dense_to_f32(float* out, const void* in, DType dt, size_t n, cudaStream_t s);
+void copy_cols(float* out, const float* in, int rows, int cols, int ld, cudaStream_t s);      // out [rows, cols] = the first cols columns of in [rows, ld]
 struct WindowAttn {
     int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
     int window = 0, keep = 0;          // window == 0: full causal
