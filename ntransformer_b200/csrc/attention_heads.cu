@@ -15,6 +15,7 @@
 #include "kernels_internal.h"
 #include "ring.cuh"
 #include <cuda_bf16.h>
+#include <algorithm>
 
 namespace nt { namespace b200 {
 
@@ -45,7 +46,8 @@ __device__ __forceinline__ void norm_rotate_head(float* row, int dim, const floa
     __syncwarp();
 }
 
-// grid (T), 256 threads; shared: cos[dims/2] | sin[dims/2] | one head per warp [8][dim]
+// grid (T, y), 256 threads: the CTAs of a token share its heads (a warp per head) and value channels, each with its own cos / sin of the
+// position; shared: cos[dims/2] | sin[dims/2] | one head per warp [8][dim]
 template <typename KT>
 __global__ void __launch_bounds__(256) head_prep_kernel(float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V, HeadPrep p,
                                                         KT* __restrict__ kc, KT* __restrict__ vc, const int* __restrict__ pos_dev, int p0) {
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(256) head_prep_kernel(float* __restrict__ Q, c
     __syncthreads();
     float* row = rows + (size_t)warp * p.dim;
     const int n_heads = p.heads + p.kv_heads;
-    for (int hh = warp; hh < n_heads; hh += 8) {
+    for (int hh = blockIdx.y * 8 + warp; hh < n_heads; hh += 8 * gridDim.y) {
         const bool is_q = hh < p.heads;
         const int h = is_q ? hh : hh - p.heads;
         const float* src = is_q ? Q + ((size_t)t * p.heads + h) * p.dim : K + ((size_t)t * p.kv_heads + h) * p.dim;
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(256) head_prep_kernel(float* __restrict__ Q, c
     }
     const int vw = p.kv_heads * p.vdim;
     const float lam = p.v_lambda ? *p.v_lambda : 0.f;
-    for (int i = threadIdx.x; i < vw; i += 256) {
+    for (int i = blockIdx.y * 256 + threadIdx.x; i < vw; i += 256 * gridDim.y) {
         float v = V[(size_t)t * vw + i];
         if (p.v_publish) p.v_publish[(size_t)t * vw + i] = v;
         if (p.v_first) v = (1.0f - lam) * v + lam * p.v_first[(size_t)t * vw + i];
@@ -112,10 +114,11 @@ void head_prep(float* Q, const float* K, const float* V, const HeadPrep& p, void
     if (tokens <= 0) return;
     const size_t smem = sizeof(float) * ((size_t)p.rot_dims + (size_t)8 * p.dim);
     NT_CHECK(smem <= 48 * 1024, "head_prep: heads wider than the kernel's shared memory");
+    const int ny = std::max(1, std::min(8, (p.heads + p.kv_heads + 7) / 8));       // a decoded token has one row: spread its heads over a few CTAs
     if (cache_dt == DType::F32)
-        launch_k(head_prep_kernel<float>, dim3(tokens), dim3(256), smem, s, Q, K, V, p, static_cast<float*>(kc), static_cast<float*>(vc), pos_dev, p0);
+        launch_k(head_prep_kernel<float>, dim3(tokens, ny), dim3(256), smem, s, Q, K, V, p, static_cast<float*>(kc), static_cast<float*>(vc), pos_dev, p0);
     else
-        launch_k(head_prep_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), smem, s, Q, K, V, p, static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc),
+        launch_k(head_prep_kernel<__nv_bfloat16>, dim3(tokens, ny), dim3(256), smem, s, Q, K, V, p, static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc),
                  pos_dev, p0);
     count_launch();
 }

@@ -518,6 +518,11 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
             }
         ffmax = std::max(ffmax, (size_t)L.wo.cols);
     }
+    if (sum_form && any_tc) {             // the gated feed-forward's fused gate / up GEMM writes the down GEMM's split input here
+        size_t ffw = 1;
+        for (const LayerSpec& S : cfg_.layers) ffw = std::max(ffw, (size_t)S.ff);
+        pf_.ws2 = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)ffw));
+    }
     if (post_form && any_tc) {            // one split workspace: rows_matmul splits its input right before the GEMM
         pf_.ws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)std::max(hidden, ffmax)));
         any_tc = false;

@@ -238,13 +238,21 @@ void Model::layer_sumnorm(int i, int T, const int* pos_dev, int p0, const RowBuf
         if (T == 1) {
             GemvMat gu[2] = {mat_of(L.gate, g), mat_of(L.up, nullptr)};
             gemv_dense(gu, 2, hidden, B.x, S.act == GluAct::RELU ? DENSE_REGLU : (S.act == GluAct::GELU_TANH ? DENSE_GEGLU : DENSE_SWIGLU), nullptr, 1.f, s);
+            rows_matmul(B.y, g, L.down, T, s);
+        } else if (pf_.ws && pf_.ws2 && spec_tc_ok(L.gate) && spec_tc_ok(L.up) && spec_tc_ok(L.down) && S.ff % 128 == 0) {
+            // gate / up GEMMs with the gated activation and the split for the down projection in the epilogue: the [T, ff]
+            // activations never reach HBM in FP32
+            TcOpts o; o.bf16 = true; o.gelu = S.act == GluAct::GELU_TANH; o.relu = S.act == GluAct::RELU;
+            split_activations(pf_.ws, B.x, T, hidden, s, true);
+            NT_CHECK(gemm_f16_tc_swiglu_ws(pf_.ws2, pf_.ws, L.gate.ptr, L.up.ptr, T, S.ff, hidden, s, o), "prefill GEMM (gate/up) rejected");
+            spec_gemm(B.y, nullptr, pf_.ws2, L.down, T, DENSE_STORE, nullptr, 1.f, s);
         } else {
             bool split_done = false;
             rows_matmul(g, B.x, L.gate, T, s, &split_done);
             rows_matmul(up, B.x, L.up, T, s, &split_done);
             glu_mul(g, g, up, (size_t)T * S.ff, S.act == GluAct::GELU_TANH, s, S.act == GluAct::RELU);
+            rows_matmul(B.y, g, L.down, T, s);
         }
-        rows_matmul(B.y, g, L.down, T, s);
         sum_rmsnorm_rows(B.x, alpha, B.y, 1.f, nullptr, nullptr, 0.f, L.ffn_norm, T, hidden, eps, s, N ? B.t[0] : nullptr, N ? N->shift_mu : nullptr,
                          N ? N->shift_state : nullptr, pos_dev, p0);
     }

@@ -358,7 +358,7 @@ bool gemm_f16_tc_ragged_supported(const void* W_f16, int N, int K, size_t row_pi
 // Variants of the tensor-core GEMM: bf16 — weights and the activation split are BF16 (safetensors families; the same 16-bit
 // layouts, only the MMA's operand format changes); gelu — the gated epilogue uses tanh-GELU instead of SiLU; col_scale / alpha —
 // the store / add epilogue writes C (+)= alpha * col_scale[n] * (A.W^T) (per-channel layer scale and residual multiplier).
-struct TcOpts { bool bf16 = false; bool gelu = false; const float* col_scale = nullptr; float alpha = 1.0f; };
+struct TcOpts { bool bf16 = false; bool gelu = false; const float* col_scale = nullptr; float alpha = 1.0f; bool relu = false; /* gated epilogue: ReLU gate */ };
 void split_activations(void* workspace, const float* A, int M, int K, cudaStream_t s, bool bf16 = false);
 bool gemm_f16_tc_ws(float* C, const void* workspace, const void* W_f16, int M, int N, int K, bool add, cudaStream_t s, const TcOpts& o = TcOpts());
 // workspace_out <- split(silu(A.Wgate^T) * (A.Wup^T)): the FFN's gate/up GEMMs with the SwiGLU + split fused in the epilogue

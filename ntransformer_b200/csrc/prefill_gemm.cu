@@ -37,8 +37,9 @@ template <int BN> struct Cfg {
     static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
 
-// the gated unit's activation: SiLU, or tanh-GELU written through exp (tanh u = 1 - 2 / (e^{2u} + 1); saturates cleanly at both ends)
+// the gated unit's activation (0 SiLU, 1 tanh-GELU, 2 ReLU): SiLU, or tanh-GELU written through exp (tanh u = 1 - 2 / (e^{2u} + 1); saturates cleanly at both ends)
 __device__ __forceinline__ float gate_act(float g, int gelu) {
+    if (gelu == 2) return fmaxf(g, 0.f);          // ReLU gate
     if (!gelu) return g / (1.0f + expf(-g));
     const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
     return 0.5f * g * (2.0f - 2.0f / (expf(2.0f * u) + 1.0f));
@@ -412,7 +413,7 @@ bool launch_gemm(float* C, __half* split_out, const void* workspace, const void*
     static const int kc_env = [] { const char* e = getenv("NT_B200_GEMM_KC"); return e ? atoi(e) : 64; }();
     const int kc_blocks = kc_env > 0 ? kc_env : K / BK;
     gemm_f16_tc_kernel<BN, MODE><<<grid, 192, Cfg<BN>::SMEM, s>>>(map_a, map_b, map_b2, C, split_out, M, (int)Mp, N, K, tiles_m, tiles_n,
-                                                                 n_tiles, n_outer, kc_blocks, o.bf16 ? 1 : 0, o.gelu ? 1 : 0, o.col_scale, o.alpha);
+                                                                 n_tiles, n_outer, kc_blocks, o.bf16 ? 1 : 0, o.relu ? 2 : (o.gelu ? 1 : 0), o.col_scale, o.alpha);
     count_launch();
     return true;
 }
