@@ -235,6 +235,7 @@ __global__ void __launch_bounds__(128) delta_rule_rows_vec_kernel(float* __restr
         const float* sa = sk + DR_TILE * dim;
         const float* sv = sa + DR_TILE * dim;
         const float* sb = sv + DR_TILE * COLS;
+#pragma unroll 4
         for (int tt = 0; tt < nt; tt++) {
             float4 kk[CH];
             float d1 = 0.f, d2 = 0.f;
@@ -323,11 +324,14 @@ void delta_rule_rows(float* out, const float* q, const float* k, const float* v,
                                            reinterpret_cast<uintptr_t>(state)) & 15) == 0;
     if (aligned) {                  // 16-byte rows: the vector form, dim / 4 lanes per column
 #define NT_DV(LN, CH) launch_rows_vec<LN, CH>(out, q, k, v, a, beta, qk, state, T, heads, kv_heads, dim, vdim, pos_dev, p0, s)
+        // lanes per column: as many as the head allows while the grid stays within about four warps per scheduler (the reduction over
+        // the lanes costs instructions; beyond that the kernel is bound by issue slots, not by latency), else half as many with two chunks each
+        const auto crowded = [&](int ln) { return (long)heads * vdim * ln / 32 > 4L * 4 * 148; };
         if (dim <= 8) NT_DV(2, 1);
         else if (dim <= 16) NT_DV(4, 1);
-        else if (dim <= 32) NT_DV(8, 1);
-        else if (dim <= 64) NT_DV(16, 1);
-        else if (dim <= 128) NT_DV(32, 1);
+        else if (dim <= 32) { if (crowded(8)) NT_DV(4, 2); else NT_DV(8, 1); }
+        else if (dim <= 64) { if (crowded(16)) NT_DV(8, 2); else NT_DV(16, 1); }
+        else if (dim <= 128) { if (crowded(32)) NT_DV(16, 2); else NT_DV(32, 1); }
         else NT_DV(32, 2);
 #undef NT_DV
         count_launch();

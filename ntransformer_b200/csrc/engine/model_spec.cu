@@ -2,7 +2,8 @@
 // loading a model folder, the per-token decode step and the batched prompt pass, written against LayerSpec so that the
 // mechanisms (windowed / soft-capped attention, whole-projection q/k norm, parallel block with layer scale, GELU-gated unit,
 // layers sharing tensors) combine freely.  Same buffers, stream, CUDA-graph replay, logits and sampler as the GGUF families
-// (engine/model.cu); the KV cache is per layer because layers may differ in width.
+// (engine/model.cu); the KV cache is per layer because layers may differ in width.  Layers of BlockForm::SUM_NORM live in
+// engine/model_sumnorm.cu.
 //
 // Arithmetic: the residual stream, norms, softmax and every accumulation are F32.  Weights stay in their stored dtype (BF16)
 // and are widened in registers, or — exact 32-bit mode — are widened once at load.  The cache stores BF16 (F32 in exact mode).

@@ -9,7 +9,10 @@
 //
 // Launches per decoded token: all projections of the layer's mixers in one GEMV launch, all their convolutions in one launch, then per
 // attention [norm / rotation / cache write] [attention] ([head mix]) [o GEMV], per delta rule [decay GEMV] [gate GEMV] [prep] [recurrence]
-// [gate + norm] [o GEMV], then [sum + norm (+ the next layer's shift)] [gate / up GEMV with the ReLU gate] [down GEMV] [sum + norm + shift].
+// [gate + norm] [o GEMV], then [sum + norm (+ the next layer's shift)] [gate / up GEMV with the ReLU gate] [down GEMV] [sum + norm + shift]:
+// 16 for a layer of two mixers, 8 for an attention layer.  Prompt rows take the tensor-core GEMMs (short matrices through their
+// zero-padded copies, the gated pair fused with its activation), the tiled attention kernel where the head widths fit it, and the
+// tiled recurrence.
 #include "model.h"
 
 #include <algorithm>
@@ -27,7 +30,7 @@ template <typename T> T* dmalloc0(size_t n) {
 constexpr size_t kScratchSlack = 256;       // floats behind RowBufs::wide for the 16-byte alignment of the buffers carved from it
 GemvMat mat_of(const Weight& w, float* y) { GemvMat m; m.W = w.ptr; m.y = y; m.out = w.rows; m.dtype = w.dtype; m.row_pitch = w.pitch; return m; }
 
-// floats per row that one mixer's intermediates take in RowBufs::wide (see carve())
+// floats per row that one mixer's intermediates take in RowBufs::wide (the buffers layer_sumnorm carves for it)
 size_t mixer_floats(const LayerSpec& S) {
     const size_t H = (size_t)S.heads, G = (size_t)S.kv_heads, D = (size_t)S.dim, V = (size_t)S.vdim;
     if (S.mixer == MixerKind::DELTA_RULE)
