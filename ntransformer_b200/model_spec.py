@@ -319,16 +319,16 @@ def tanolorn_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype
 
 
 # ---- Savidra (layer-spec family, model folders): synthetic configurations and random device weights for benchmarks ----
-def savidra_config(vocab=32000, width=2048, pattern=("parallel", "attention", "parallel", "attention"), ff=4096, v_mix=(1, 3), alpha=2.0, eps=1e-6,
+def savidra_config(vocab=32000, width=2048, pattern=("parallel", "attention", "parallel", "attention"), ff=4096, v_mix=(1, 3), alpha=1.5, eps=1e-5,
                    left=None, right=None, attn=None, left_scale=1.0, right_scale=1.0):
     """The family's config.json as a dict.  pattern: mixer type per layer ("parallel": head-mixed attention beside the gated delta rule;
     "attention": sink attention); left / right / attn override the mixers' sizes; v_mix: the attention layers whose values blend with the
     first of them; ff: feed-forward width (0: none)."""
-    lf = dict(heads=16, kv_heads=2, dim=128, vdim=64, conv=4, rot_dims=128, base=1e6, factor=8.0)
+    lf = dict(heads=16, kv_heads=2, dim=128, vdim=64, conv=3, rot_dims=128, base=5e5, factor=4.0)
     lf.update(left or {})
     rt = dict(heads=16, kv_heads=16, dim=64, vdim=128, conv=4, decay_rank=64, gate_rank=64)
     rt.update(right or {})
-    at = dict(heads=16, kv_heads=4, dim=128, vdim=128, rot_dims=64, base=1e6)
+    at = dict(heads=16, kv_heads=4, dim=128, vdim=128, rot_dims=64, base=5e5)
     at.update(attn or {})
     layers = []
     for i, typ in enumerate(pattern):
